@@ -1,0 +1,36 @@
+// Declarations shared by the contraction kernels (CUDA-core and tcgen05 paths) and their C ABI.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+// Fused epilogue applied to one accumulator value; node order of the chains it replaces:
+//   BIAS          MatMul/Gemm/Conv -> Add(bias)
+//   BIAS_RELU     ... -> Relu
+//   BIAS_GELU     ... -> Div(sqrt2) -> Erf -> Add 1 -> Mul x -> Mul 0.5
+//   BIAS_RESIDUAL ... -> Add(residual)
+//   SCALE         MatMul -> Mul(constant)
+__device__ __forceinline__ float apply_epilogue(int epi, float acc, float bias, float residual, float scale) {
+  switch (epi) {
+    case B200_EPI_BIAS: return acc + bias;
+    case B200_EPI_BIAS_RELU: return fmaxf(acc + bias, 0.f);
+    case B200_EPI_BIAS_GELU: return gelu_erf(acc + bias);
+    case B200_EPI_BIAS_RESIDUAL: return (acc + bias) + residual;
+    case B200_EPI_SCALE: return acc * scale;
+    default: return acc;
+  }
+}
+
+int gemm_simt(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
+              const float *residual, float *Y);
+int conv2d_simt(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias,
+                float *Y, int64_t OH, int64_t OW);
+
+// tcgen05 path. `can_*` say whether the operands meet the TMA addressing rules (16-byte aligned
+// bases and row strides, K a multiple of 4); the launchers assume they do.
+bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, const float *Y);
+int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
+            const float *residual, float *Y);
+
+}  // namespace b200

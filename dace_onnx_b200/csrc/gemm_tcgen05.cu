@@ -1,0 +1,618 @@
+// Tensor-core GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma (kind::tf32) -> TMEM -> epilogue.
+//
+// One persistent CTA per SM walks a static list of 128 x BN output tiles. Inside a CTA the warps
+// are specialised:
+//   warp 0      TMA producer: one lane issues cp.async.bulk.tensor loads of the A and B k-blocks
+//               (128B-swizzled, 32 fp32 of K per block) into a ring of shared-memory stages;
+//   warp 1      MMA issuer: allocates TMEM, one lane issues tcgen05.mma for each 8-wide k-step
+//               and commits stage release / accumulator-ready events to mbarriers;
+//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (row = TMEM lane, one row per thread),
+//               apply the fused epilogue (bias / ReLU / erf-Gelu / residual / scale) and store;
+//   warps 6-9   (3xTF32 mode only) split warps: rewrite each landed stage in place as
+//               hi = tf32(x) and write lo = tf32(x - hi) beside it, so that the issuer can run
+//               lo*hi + hi*lo + hi*hi into the same fp32 accumulator (fp32-accurate products).
+// Two TMEM accumulators alternate so that the epilogue of tile i overlaps the MMAs of tile i+1.
+//
+// Every mbarrier wait is bounded by a cycle budget; on expiry the CTA sets a bit in the device
+// status word, all roles leave their loops, TMEM is released and the kernel returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "contract.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // fp32 elements per k-block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;                    // K of one kind::tf32 instruction
+constexpr int A_STAGE_BYTES = BM * BK * 4;   // 16 KiB
+constexpr long long kWaitCycleBudget = 4000000000LL;  // ~2 s at 1.9 GHz
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false when the CTA is aborting (budget exceeded here or in another role).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          unsigned *status, unsigned code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 0xffu) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycleBudget) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, descriptor version 1 (sm_100).
+//   K-major operand: rows of 32 fp32 = 128 B, 16-byte chunks XOR-swizzled with the row index
+//     (layout type 2, SWIZZLE_128B); 8-row groups 1024 B apart: LBO unused (=16 B), SBO = 1024 B.
+//   MN-major 32-bit operand: 32-wide column chunks, each [k][128 B], chunks `lbo` bytes apart. The
+//     only layout the tensor core accepts for it swizzles 32-byte chunks with (k mod 4)
+//     (layout type 1, SWIZZLE_128B_BASE32B; TMA writes it with SWIZZLE_128B_ATOM_32B), so the
+//     repeating group along K is 4 rows = 512 B: SBO = 512 B.
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::tf32: fp32 accumulate, TF32 A and B, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ float to_tf32_rna(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+struct GemmParams {
+  int64_t M, N;
+  int num_kb;
+  int num_m_tiles, num_n_tiles;
+  int64_t num_tiles;
+  int batch_inner;
+  int a_bi, a_bo, b_bi, b_bo;  // 1 when the operand advances with that batch index, 0 when broadcast
+  int64_t ldy, y_stride_outer, y_stride_inner;
+  int epilogue;
+  float scale;
+  const float *bias;
+  const float *residual;
+  float *Y;
+  unsigned *status;
+};
+
+// k-blocks per in-core accumulation chunk in 3xTF32 mode (2 x 32 = 64 values of K, 24 MMAs).
+constexpr int kSplitChunkKb = 2;
+
+// Epilogue + store of 32 consecutive columns [n0, n0+32) of output row m held in registers.
+__device__ __forceinline__ void store_row32(const GemmParams &p, const float *v, int64_t m, int64_t row_off,
+                                            int64_t n0, bool vec_ok) {
+  if (m >= p.M || n0 >= p.N) return;
+  float *yrow = p.Y + row_off + n0;
+  const float *rrow = p.residual ? p.residual + row_off + n0 : nullptr;
+  if (vec_ok && n0 + 32 <= p.N) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (p.bias) b4 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j));
+      if (rrow) r4 = *reinterpret_cast<const float4 *>(rrow + j);
+      float4 o;
+      o.x = apply_epilogue(p.epilogue, v[j + 0], b4.x, r4.x, p.scale);
+      o.y = apply_epilogue(p.epilogue, v[j + 1], b4.y, r4.y, p.scale);
+      o.z = apply_epilogue(p.epilogue, v[j + 2], b4.z, r4.z, p.scale);
+      o.w = apply_epilogue(p.epilogue, v[j + 3], b4.w, r4.w, p.scale);
+      *reinterpret_cast<float4 *>(yrow + j) = o;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (n0 + j < p.N)
+        yrow[j] = apply_epilogue(p.epilogue, v[j], p.bias ? __ldg(p.bias + n0 + j) : 0.f, rrow ? rrow[j] : 0.f,
+                                 p.scale);
+    }
+  }
+}
+
+template <int BN, bool SPLIT3>
+struct Cfg {
+  static constexpr int kBStageBytes = BN * BK * 4;
+  static constexpr int kStageBytes = (A_STAGE_BYTES + kBStageBytes) * (SPLIT3 ? 2 : 1);
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; BN is a power of two
+  static constexpr int kThreads = SPLIT3 ? 320 : 192;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int BN, bool B_MN, bool SPLIT3>
+__global__ void __launch_bounds__(Cfg<BN, SPLIT3>::kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemmParams p) {
+  using C = Cfg<BN, SPLIT3>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors address.
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
+  // barrier layout: full[kStages] empty[kStages] split[kStages] tmem_full[2] tmem_empty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_split = bar_empty + 8 * kStages;
+  const uint32_t bar_tfull = bar_split + 8 * kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_split + 8 * s, 128);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&s_tmem_base), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int *abort_flag = &s_abort;
+
+  auto stage_a = [&](int s) { return smem_base + s * C::kStageBytes; };
+  auto stage_b = [&](int s) { return smem_base + s * C::kStageBytes + A_STAGE_BYTES; };
+  auto stage_a_lo = [&](int s) { return smem_base + s * C::kStageBytes + A_STAGE_BYTES + C::kBStageBytes; };
+  auto stage_b_lo = [&](int s) { return smem_base + s * C::kStageBytes + 2 * A_STAGE_BYTES + C::kBStageBytes; };
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int64_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        const int n_t = (int)(tile % p.num_n_tiles);
+        const int64_t r = tile / p.num_n_tiles;
+        const int m_t = (int)(r % p.num_m_tiles);
+        const int64_t batch = r / p.num_m_tiles;
+        const int bo = (int)(batch / p.batch_inner), bi = (int)(batch % p.batch_inner);
+        bool ok = true;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
+          mbar_expect_tx(bar_full + 8 * s, A_STAGE_BYTES + C::kBStageBytes);
+          tma_load_4d(stage_a(s), &map_a, bar_full + 8 * s, kb * BK, m_t * BM, bi * p.a_bi, bo * p.a_bo);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j)
+              tma_load_4d(stage_b(s) + j * (BK * 128), &map_b, bar_full + 8 * s, n_t * BN + 32 * j, kb * BK,
+                          bi * p.b_bi, bo * p.b_bo);
+          } else {
+            tma_load_4d(stage_b(s), &map_b, bar_full + 8 * s, kb * BK, n_t * BN, bi * p.b_bi, bo * p.b_bo);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    // The K loop is cut into chunks; each chunk accumulates into its own TMEM buffer (the two
+    // buffers alternate). In TF32 mode one chunk is the whole K. In 3xTF32 mode a chunk is
+    // kSplitChunkKb k-blocks: the tensor core adds into its accumulator with round-toward-zero, an
+    // error that grows with the number of additions times |accumulator|, so the long sum is
+    // formed by the epilogue warps in registers (round-to-nearest) from short in-core sums.
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN, B_MN);
+      const int chunk = SPLIT3 ? kSplitChunkKb : p.num_kb;
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += chunk) {
+          if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 2u))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const int kb_end = kb0 + chunk < p.num_kb ? kb0 + chunk : p.num_kb;
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            if (!(ok = mbar_wait((SPLIT3 ? bar_split : bar_full) + 8 * s, ph, abort_flag, p.status, 4u))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint32_t a_off = kk * UMMA_K * 4;                     // 32 B inside the swizzle row
+              const uint32_t b_off = B_MN ? kk * 1024 : kk * UMMA_K * 4;  // next 8 k-rows, or 32 B
+              const uint32_t b_lbo = B_MN ? BK * 128 : 16;
+              const uint32_t b_sbo = B_MN ? 512 : 1024;
+              const uint32_t b_layout = B_MN ? kLayoutSw128Base32 : kLayoutSw128;
+              const uint64_t a_hi = make_smem_desc(stage_a(s) + a_off, 16, 1024, kLayoutSw128);
+              const uint64_t b_hi = make_smem_desc(stage_b(s) + b_off, b_lbo, b_sbo, b_layout);
+              const uint32_t accumulate = (kb > kb0 || kk > 0) ? 1u : 0u;  // 0 overwrites the accumulator
+              if (SPLIT3) {
+                const uint64_t a_lo = make_smem_desc(stage_a_lo(s) + a_off, 16, 1024, kLayoutSw128);
+                const uint64_t b_lo = make_smem_desc(stage_b_lo(s) + b_off, b_lbo, b_sbo, b_layout);
+                umma_tf32(d_tmem, a_lo, b_hi, idesc, accumulate);  // small terms first
+                umma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
+                umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+              } else {
+                umma_tf32(d_tmem, a_hi, b_hi, idesc, accumulate);
+              }
+            }
+            umma_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(bar_tfull + 8 * acc);  // this chunk's accumulator is complete
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------- epilogue -------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    const bool vec_ok = (p.ldy % 4 == 0) && (p.y_stride_outer % 4 == 0) && (p.y_stride_inner % 4 == 0) &&
+                        ((reinterpret_cast<uintptr_t>(p.Y) & 15u) == 0) &&
+                        (!p.residual || (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0);
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      const int n_t = (int)(tile % p.num_n_tiles);
+      const int64_t r = tile / p.num_n_tiles;
+      const int m_t = (int)(r % p.num_m_tiles);
+      const int64_t batch = r / p.num_m_tiles;
+      const int64_t bo = batch / p.batch_inner, bi = batch % p.batch_inner;
+      const int64_t m = (int64_t)m_t * BM + quarter * 32 + lane;
+      const int64_t row_off = bo * p.y_stride_outer + bi * p.y_stride_inner + m * p.ldy;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if (SPLIT3) {
+        // Sum the per-chunk accumulators in registers, then apply the epilogue once.
+        float sum[BN];
+#pragma unroll
+        for (int j = 0; j < BN; ++j) sum[j] = 0.f;
+        for (int kb0 = 0; kb0 < p.num_kb; kb0 += kSplitChunkKb) {
+          if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + (uint32_t)(acc * BN + c0), v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(v[j]);
+          }
+          tc_fence_before();
+          mbar_arrive(bar_tempty + 8 * acc);
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32)
+          store_row32(p, &sum[c0], m, row_off, (int64_t)n_t * BN + c0, vec_ok);
+      } else {
+        if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          float f[32];
+          tmem_ld32(lane_addr + (uint32_t)(acc * BN + c0), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          store_row32(p, f, m, row_off, (int64_t)n_t * BN + c0, vec_ok);
+        }
+        tc_fence_before();
+        mbar_arrive(bar_tempty + 8 * acc);  // 128 arrivals release the accumulator
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else if (SPLIT3) {
+    // ------------------------------- 3xTF32 split warps -------------------------------
+    const int t = threadIdx.x - 192;  // 0..127
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 16u))) break;
+        // A and B tiles are contiguous ([A | B | A_lo | B_lo]); the split is elementwise, so the
+        // swizzled placement of each 16-byte chunk is preserved by writing at the same offset.
+        float4 *src = reinterpret_cast<float4 *>(smem + (size_t)s * C::kStageBytes);
+        float4 *dst_lo = reinterpret_cast<float4 *>(smem + (size_t)s * C::kStageBytes + A_STAGE_BYTES + C::kBStageBytes);
+        constexpr int kVecs = (A_STAGE_BYTES + C::kBStageBytes) / 16;
+#pragma unroll 4
+        for (int i = t; i < kVecs; i += 128) {
+          const float4 x = src[i];
+          float4 hi, lo;
+          hi.x = to_tf32_rna(x.x); hi.y = to_tf32_rna(x.y); hi.z = to_tf32_rna(x.z); hi.w = to_tf32_rna(x.w);
+          lo.x = to_tf32_rna(x.x - hi.x); lo.y = to_tf32_rna(x.y - hi.y);
+          lo.z = to_tf32_rna(x.z - hi.z); lo.w = to_tf32_rna(x.w - hi.w);
+          src[i] = hi;
+          dst_lo[i] = lo;
+        }
+        // Make the generic-proxy writes visible to the tensor core (async proxy) before signalling.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(bar_split + 8 * s);
+        if (++s == kStages) { s = 0; ph ^= 1; }
+      }
+    }
+  }
+
+  // Teardown: all roles meet, then the allocating warp returns the TMEM columns.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
+    // Give loads that were already issued time to land before the CTA's shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side: tensor-map encoding and launch
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;  // process-wide driver entry point; identical for every device
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// rank-4 fp32 map: dims {d0 (contiguous), d1, d2, d3}, byte strides for d1..d3, zero OOB fill.
+int encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+               uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t box[4] = {box0, box1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200_ECUDA,
+                "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} strides {%llu,%llu,%llu} box {%u,%u}",
+                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                (unsigned long long)dims[3], (unsigned long long)strides_bytes[0],
+                (unsigned long long)strides_bytes[1], (unsigned long long)strides_bytes[2], box0, box1);
+  return B200_OK;
+}
+
+// A batch axis that is broadcast (stride 0) or trivial (extent 1) is encoded with extent 1 and a
+// valid dummy stride; the kernel then always passes coordinate 0 on it.
+void batch_axis(int64_t extent, int64_t stride_elems, uint64_t fallback_bytes, uint64_t *dim, uint64_t *stride_bytes,
+                int *advances) {
+  if (extent > 1 && stride_elems != 0) {
+    *dim = (uint64_t)extent;
+    *stride_bytes = (uint64_t)stride_elems * 4;
+    *advances = 1;
+  } else {
+    *dim = 1;
+    *stride_bytes = fallback_bytes;
+    *advances = 0;
+  }
+}
+
+template <int BN, bool B_MN, bool SPLIT3>
+int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
+  using C = Cfg<BN, SPLIT3>;
+  auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+    return fail(B200_ECUDA, "gemm(tc): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  const int64_t grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  kern<<<(unsigned)grid, C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
+  return check_launch("gemm_tc");
+}
+
+template <bool B_MN, bool SPLIT3>
+int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
+  switch (bn) {
+    case 64: return launch_cfg<64, B_MN, SPLIT3>(st, ma, mb, p);
+    case 128: return launch_cfg<128, B_MN, SPLIT3>(st, ma, mb, p);
+    case 256:
+      if constexpr (!SPLIT3) return launch_cfg<256, B_MN, false>(st, ma, mb, p);
+  }
+  return fail(B200_EINVAL, "gemm(tc): no kernel for BN=%d", bn);
+}
+
+int pick_bn(int64_t N, bool split3) {
+  const int cands[3] = {256, 128, 64};
+  int best = 64;
+  double best_cost = 1e30;
+  for (int i = split3 ? 1 : 0; i < 3; ++i) {
+    const int bn = cands[i];
+    const int64_t tiles = (N + bn - 1) / bn;
+    // padded work, with a mild preference for wide tiles (fewer A re-reads, better MMA efficiency)
+    const double cost = (double)(tiles * bn) * (bn == 256 ? 1.0 : bn == 128 ? 1.04 : 1.15);
+    if (cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, const float *Y) {
+  auto ok4 = [](int64_t v) { return v % 4 == 0; };
+  if (d.M < 1 || d.N < 1 || d.K < 1) return false;
+  if (!aligned16(A) || !aligned16(B)) return false;
+  if (!ok4(d.lda) || !ok4(d.ldb)) return false;
+  if (!ok4(d.a_stride_outer) || !ok4(d.a_stride_inner) || !ok4(d.b_stride_outer) || !ok4(d.b_stride_inner))
+    return false;
+  if (d.lda < d.K) return false;
+  if (d.trans_b ? d.ldb < d.K : d.ldb < d.N) return false;
+  if (d.M > 0x7fffffffLL || d.N > 0x7fffffffLL || d.K > 0x7fffffffLL) return false;
+  if (d.batch_outer > 0x7fffffffLL || d.batch_inner > 0x7fffffffLL) return false;
+  (void)Y;
+  return true;
+}
+
+int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
+            const float *residual, float *Y) {
+  const bool split3 = d.math_mode == B200_MATH_FP32X3;
+  const int bn = pick_bn(d.N, split3);
+
+  CUtensorMap ma, mb;
+  GemmParams p;
+  {
+    uint64_t dims[4] = {(uint64_t)d.K, (uint64_t)d.M, 1, 1};
+    uint64_t str[3] = {(uint64_t)d.lda * 4, 0, 0};
+    const uint64_t fb = (uint64_t)d.lda * 4 * (uint64_t)d.M;
+    batch_axis(d.batch_inner, d.a_stride_inner, fb, &dims[2], &str[1], &p.a_bi);
+    batch_axis(d.batch_outer, d.a_stride_outer, fb, &dims[3], &str[2], &p.a_bo);
+    if (int rc = encode_map(&ma, A, dims, str, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  }
+  {
+    uint64_t dims[4], str[3];
+    uint64_t fb;
+    if (d.trans_b) {
+      dims[0] = (uint64_t)d.K; dims[1] = (uint64_t)d.N;
+      fb = (uint64_t)d.ldb * 4 * (uint64_t)d.N;
+    } else {
+      dims[0] = (uint64_t)d.N; dims[1] = (uint64_t)d.K;
+      fb = (uint64_t)d.ldb * 4 * (uint64_t)d.K;
+    }
+    str[0] = (uint64_t)d.ldb * 4;
+    batch_axis(d.batch_inner, d.b_stride_inner, fb, &dims[2], &str[1], &p.b_bi);
+    batch_axis(d.batch_outer, d.b_stride_outer, fb, &dims[3], &str[2], &p.b_bo);
+    if (int rc = encode_map(&mb, B, dims, str, d.trans_b ? BK : 32, d.trans_b ? (uint32_t)bn : BK,
+                            d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+      return rc;
+  }
+  p.M = d.M;
+  p.N = d.N;
+  p.num_kb = (int)((d.K + BK - 1) / BK);
+  p.num_m_tiles = (int)((d.M + BM - 1) / BM);
+  p.num_n_tiles = (int)((d.N + bn - 1) / bn);
+  p.batch_inner = (int)d.batch_inner;
+  p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * d.batch_outer * d.batch_inner;
+  p.ldy = d.ldy;
+  p.y_stride_outer = d.y_stride_outer;
+  p.y_stride_inner = d.y_stride_inner;
+  p.epilogue = d.epilogue;
+  p.scale = d.scale;
+  p.bias = bias;
+  p.residual = residual;
+  p.Y = Y;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(B200_ECUDA, "gemm(tc): device status word unavailable");
+
+  if (d.trans_b) {
+    return split3 ? launch_bn<false, true>(st, bn, ma, mb, p) : launch_bn<false, false>(st, bn, ma, mb, p);
+  }
+  return split3 ? launch_bn<true, true>(st, bn, ma, mb, p) : launch_bn<true, false>(st, bn, ma, mb, p);
+}
+
+}  // namespace b200

@@ -1,0 +1,150 @@
+"""BERT encoder runner: the exported ONNX subgraph of `transformers` BertLayer executed through the C ABI.
+
+This is the caller side of the hot path for the BERT configurations: what DaCeML's
+`DaceModule(BertLayer)` runs after node expansion (daceml/pytorch/module.py:212-295 builds it,
+tests/pytorch/test_bert_encoder.py:10-50 exercises it), with the elementwise chains folded into
+the contraction epilogues where the graph allows it:
+
+    MatMul(x, Transpose(W)) + Add(bias)                      -> gemm, trans_b, EPI_BIAS
+    ... + Add(residual)                                      -> EPI_BIAS_RESIDUAL
+    ... + Div/Erf/Add/Mul/Mul (Gelu)                         -> EPI_BIAS_GELU
+    MatMul(q, k^T) + Mul(1/sqrt(d))                          -> batched gemm, EPI_SCALE
+    Reshape/Transpose [0,2,1,3] either side of attention     -> strided batch addressing (no copy)
+    ReduceMean..Add (9 nodes)                                -> layernorm
+
+Torch provides device buffers, streams and (for several GPUs) the process group; all arithmetic
+is in libb200ops.
+"""
+import math
+
+import torch
+
+from . import ops
+from ._lib import EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_SCALE
+
+
+class BertEncoderB200:
+    """N identical-shape BERT encoder layers on one GPU.
+
+    `layers` is a list of dicts with keys wq,bq,wk,bk,wv,bv,wo,bo,ln1_g,ln1_b,wi,bi,wo2,bo2,
+    ln2_g,ln2_b (Linear weights in torch layout [out, in]). The batch is processed in micro-batches
+    of `micro_batch` sequences so that the materialised [b, heads, S, S] score tensor stays bounded.
+    """
+
+    def __init__(self, layers, heads, eps=1e-12, device="cuda:0", math_mode="fp32x3", micro_batch=128):
+        self.device = torch.device(device)
+        self.heads = heads
+        self.eps = float(eps)
+        self.math_mode = math_mode
+        self.micro_batch = int(micro_batch)
+        self.hidden = layers[0]["wq"].shape[0]
+        self.ffn = layers[0]["wi"].shape[0]
+        if self.hidden % heads:
+            raise ValueError("hidden size must be a multiple of the head count")
+        self.head_dim = self.hidden // heads
+        dev = lambda t: t.detach().to(self.device, torch.float32).contiguous()  # noqa: E731
+        self.layers = []
+        for p in layers:
+            self.layers.append(dict(
+                # the three projections share their input: one GEMM against the stacked weight rows
+                wqkv=dev(torch.cat([p["wq"], p["wk"], p["wv"]], 0)), bqkv=dev(torch.cat([p["bq"], p["bk"], p["bv"]], 0)),
+                wo=dev(p["wo"]), bo=dev(p["bo"]), ln1_g=dev(p["ln1_g"]), ln1_b=dev(p["ln1_b"]),
+                wi=dev(p["wi"]), bi=dev(p["bi"]), wo2=dev(p["wo2"]), bo2=dev(p["bo2"]),
+                ln2_g=dev(p["ln2_g"]), ln2_b=dev(p["ln2_b"])))
+        self._buf_key = None
+        self._buf = None
+        self.launches = 0          # C-ABI kernel launches issued so far
+        self.timeline = None       # when a list: (kind, flops, bytes, start_event, end_event) per launch
+
+    # -- scratch --------------------------------------------------------------------------------
+    def _buffers(self, mb, seq):
+        key = (mb, seq)
+        if self._buf_key != key:
+            h, f, nh = self.hidden, self.ffn, self.heads
+            e = lambda *s: torch.empty(s, device=self.device, dtype=torch.float32)  # noqa: E731
+            self._buf = dict(qkv=e(mb, seq, 3 * h), scores=e(mb, nh, seq, seq), probs=e(mb, nh, seq, seq),
+                             ctx=e(mb, seq, h), attn=e(mb, seq, h), h1=e(mb, seq, h), inter=e(mb, seq, f),
+                             out=e(mb, seq, h), ping=e(mb, seq, h), pong=e(mb, seq, h))
+            self._buf_key = key
+        return self._buf
+
+    def _timed(self, kind, flops, nbytes, fn):
+        self.launches += 1
+        if self.timeline is None:
+            return fn()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = fn()
+        e.record()
+        self.timeline.append((kind, flops, nbytes, s, e))
+        return r
+
+    # -- one layer on one micro-batch -------------------------------------------------------------
+    def _layer(self, x, y, w, buf, b, seq):
+        h, f, nh, d, mm = self.hidden, self.ffn, self.heads, self.head_dim, self.math_mode
+        t = b * seq
+        x2 = x.view(t, h)
+        qkv, scores, probs, ctx = buf["qkv"][:b], buf["scores"][:b], buf["probs"][:b], buf["ctx"][:b]
+        attn, h1, inter, out = buf["attn"][:b], buf["h1"][:b], buf["inter"][:b], buf["out"][:b]
+
+        self._timed("gemm", 2 * t * 3 * h * h, 0, lambda: ops.matmul(
+            x2, w["wqkv"], out=qkv.view(t, 3 * h), trans_b=True, epilogue=EPI_BIAS, bias=w["bqkv"], math_mode=mm))
+        # scores[b,n] = q[b,:,n,:] @ k[b,:,n,:]^T * 1/sqrt(d), heads addressed inside qkv
+        self._timed("gemm_qk", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
+            qkv, qkv[..., h:], scores, batch_outer=b, batch_inner=nh, M=seq, N=seq, K=d, lda=3 * h, ldb=3 * h,
+            ldy=seq, a_strides=(seq * 3 * h, d), b_strides=(seq * 3 * h, d), y_strides=(nh * seq * seq, seq * seq),
+            trans_b=True, epilogue=EPI_SCALE, scale=1.0 / math.sqrt(d), math_mode=mm))
+        self._timed("softmax", 0, 8 * b * nh * seq * seq, lambda: ops.softmax(scores, 3, out=probs))
+        # ctx[b,:,n,:] = probs[b,n] @ v[b,:,n,:]; written straight into [b, S, hidden]
+        self._timed("gemm_pv", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
+            probs, qkv[..., 2 * h:], ctx, batch_outer=b, batch_inner=nh, M=seq, N=d, K=seq, lda=seq, ldb=3 * h,
+            ldy=h, a_strides=(nh * seq * seq, seq * seq), b_strides=(seq * 3 * h, d), y_strides=(seq * h, d),
+            trans_b=False, math_mode=mm))
+        self._timed("gemm", 2 * t * h * h, 0, lambda: ops.matmul(
+            ctx.view(t, h), w["wo"], out=attn.view(t, h), trans_b=True, epilogue=EPI_BIAS_RESIDUAL, bias=w["bo"],
+            residual=x2, math_mode=mm))
+        self._timed("layernorm", 0, 8 * t * h, lambda: ops.layernorm(attn, w["ln1_g"], w["ln1_b"], self.eps, out=h1))
+        self._timed("gemm", 2 * t * f * h, 0, lambda: ops.matmul(
+            h1.view(t, h), w["wi"], out=inter.view(t, f), trans_b=True, epilogue=EPI_BIAS_GELU, bias=w["bi"],
+            math_mode=mm))
+        self._timed("gemm", 2 * t * f * h, 0, lambda: ops.matmul(
+            inter.view(t, f), w["wo2"], out=out.view(t, h), trans_b=True, epilogue=EPI_BIAS_RESIDUAL, bias=w["bo2"],
+            residual=h1.view(t, h), math_mode=mm))
+        self._timed("layernorm", 0, 8 * t * h, lambda: ops.layernorm(out, w["ln2_g"], w["ln2_b"], self.eps, out=y))
+        return y
+
+    # -- whole encoder ------------------------------------------------------------------------------
+    def forward_device(self, x, out=None):
+        """x: [B, S, hidden] fp32 on this encoder's device. Returns [B, S, hidden] on the device."""
+        if x.device != self.device or x.dtype != torch.float32 or x.dim() != 3 or x.shape[2] != self.hidden:
+            raise ValueError("expected a float32 [B, S, %d] tensor on %s" % (self.hidden, self.device))
+        x = x.contiguous()
+        bsz, seq, _ = x.shape
+        if out is None:
+            out = torch.empty_like(x)
+        mb = min(self.micro_batch, max(bsz, 1))
+        buf = self._buffers(mb, seq)
+        for b0 in range(0, bsz, mb):
+            b = min(mb, bsz - b0)
+            cur = x[b0:b0 + b]
+            for li, w in enumerate(self.layers):
+                last = li + 1 == len(self.layers)
+                dst = out[b0:b0 + b] if last else (buf["ping"][:b] if li % 2 == 0 else buf["pong"][:b])
+                cur = self._layer(cur, dst, w, buf, b, seq)
+        return out
+
+    def __call__(self, x_host, out_host=None):
+        """Host entry: copies a (preferably pinned) host tensor in, runs, copies the result back."""
+        x = x_host.to(self.device, non_blocking=True)
+        y = self.forward_device(x)
+        if out_host is None:
+            return y.cpu()
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host
+
+    # -- work model (algorithmic figures used by the roofline report) ---------------------------------
+    def flops_per_sequence(self, seq):
+        h, f, nh, d = self.hidden, self.ffn, self.heads, self.head_dim
+        per_layer = 2 * seq * (3 * h * h + h * h + 2 * f * h) + 4 * nh * seq * seq * d
+        return per_layer * len(self.layers)

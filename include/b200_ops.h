@@ -1,0 +1,157 @@
+/*
+ * b200_ops.h -- C ABI of libb200ops.so: hand-written sm_100a CUDA kernels for the ONNX
+ * library-node hot path of DaCeML (MatMul / Gemm / Conv, Softmax / LogSoftmax, the
+ * LayerNormalization and Gelu node chains, and the Add/Sub/Mul/Div/Pow/Sqrt/Erf/Relu nodes).
+ *
+ * Conventions (all entry points):
+ *   - every tensor pointer is a DEVICE pointer to contiguous row-major fp32 unless a stride
+ *     argument says otherwise; the caller owns every buffer, the library never allocates,
+ *     frees or caches device memory, and never writes its inputs;
+ *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered on it, the
+ *     library never synchronises the host and never uses the default stream implicitly;
+ *   - the return value is 0 on success or a negative B200_E* code; the message is available
+ *     from b200_last_error_string() (thread-local). Nothing exits or throws across the ABI;
+ *   - shapes/strides are int64_t counts of ELEMENTS.
+ *
+ * Each entry point replaces the GPU expansion of one DaCeML node type; the citation names the
+ * `pure` expansion (path inside spcl/dace-onnx) whose results it must reproduce.
+ */
+#ifndef B200_OPS_H
+#define B200_OPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)      /* bad pointer / shape / attribute */
+#define B200_EUNSUPPORTED (-2) /* valid ONNX, but outside what this library implements */
+#define B200_ECUDA (-3)       /* a CUDA runtime/driver call failed (launch, tensor-map encode) */
+#define B200_EWORKSPACE (-4)  /* caller-provided workspace too small */
+#define B200_EDEVICE (-5)     /* a kernel reported a bounded-wait expiry (see b200_device_status) */
+
+/* Arithmetic mode of the contraction kernels. */
+#define B200_MATH_FP32X3 0 /* tensor cores, 3xTF32 split (hi*hi + hi*lo + lo*hi), fp32 accumulate: fp32-accurate */
+#define B200_MATH_TF32 1   /* tensor cores, single TF32 pass; ~1e-3 relative error, opt-in */
+#define B200_MATH_FP32 2   /* CUDA-core fp32 FMA kernel; any shape/alignment */
+
+/* Fused epilogues of the contraction kernels: Y = epi(acc). */
+#define B200_EPI_NONE 0          /* Y = acc */
+#define B200_EPI_BIAS 1          /* Y = acc + bias[n]                      (MatMul -> Add, Gemm C, Conv B) */
+#define B200_EPI_BIAS_RELU 2     /* Y = max(acc + bias[n], 0)              (-> Relu) */
+#define B200_EPI_BIAS_GELU 3     /* t = acc + bias[n]; Y = t*0.5*(1+erf(t/sqrt(2)))  (Div,Erf,Add,Mul,Mul chain) */
+#define B200_EPI_BIAS_RESIDUAL 4 /* Y = acc + bias[n] + residual[m,n]      (-> Add, Add) */
+#define B200_EPI_SCALE 5         /* Y = acc * scale                        (-> Mul by a scalar constant) */
+
+/* Elementwise binary / unary operator codes. */
+#define B200_ADD 0
+#define B200_SUB 1
+#define B200_MUL 2
+#define B200_DIV 3
+#define B200_POW 4
+#define B200_SQRT 0
+#define B200_ERF 1
+#define B200_RELU 2
+#define B200_GELU 3 /* fused Div(sqrt2) -> Erf -> Add 1 -> Mul x -> Mul 0.5 chain */
+
+B200_API int b200_version(void);
+B200_API const char *b200_last_error_string(void);
+
+/* Reads and clears the device-side status word that kernels with bounded waits set when a wait
+ * expires (0 = clean). Synchronises the device: for tests and post-run checks, not hot paths. */
+B200_API int b200_device_status(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Contractions.
+ * b200_gemm_f32 replaces ONNXMatMul (daceml/onnx/op_implementations/pure_implementations.py:130-235,
+ * numpy matmul with batch broadcasting lowered to an einsum) and ONNXGemm (same file :433-459,
+ * Y = A @ B^T + C with alpha=beta=1, transA=0, transB=1).
+ *
+ *   for every batch (bo, bi) in [0,batch_outer) x [0,batch_inner):
+ *     Y_b[M,N] = epi( A_b[M,K] @ op(B_b) )
+ *   A_b = A + bo*a_stride_outer + bi*a_stride_inner, rows lda apart (K contiguous);
+ *   B_b likewise; trans_b=1: B_b is [N,K] with rows ldb apart; trans_b=0: B_b is [K,N];
+ *   Y_b rows ldy apart. A batch stride of 0 broadcasts that operand (numpy semantics).
+ *   bias has N entries (may be NULL for EPI_NONE/EPI_SCALE); residual addresses like Y.
+ * The two-level batch lets attention heads be addressed in place ([B,S,heads,64] views).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b200_gemm_desc {
+  int64_t batch_outer, batch_inner;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldy;
+  int64_t a_stride_outer, a_stride_inner;
+  int64_t b_stride_outer, b_stride_inner;
+  int64_t y_stride_outer, y_stride_inner;
+  int32_t trans_b;
+  int32_t epilogue;
+  float scale;
+  int32_t math_mode;
+} b200_gemm_desc;
+
+B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
+                  const float *bias, const float *residual, float *Y);
+
+/* ONNXConv (daceml/onnx/op_implementations/img_op_implementations.py:164-326): NCHW x OIHW
+ * cross-correlation, group=1, dilation=1, symmetric zero padding (the padded form is what
+ * daceml/transformation/pad_conv_fusion.py:77-95 folds into the node). bias may be NULL.
+ * epilogue: B200_EPI_NONE / B200_EPI_BIAS / B200_EPI_BIAS_RELU.
+ * workspace: b200_conv2d_workspace_bytes() bytes of device scratch (may be 0 -> NULL allowed). */
+typedef struct b200_conv_desc {
+  int64_t N, C, H, W;   /* input  X[N,C,H,W] */
+  int64_t M, KH, KW;    /* filter W[M,C,KH,KW] */
+  int64_t pad_h, pad_w; /* symmetric */
+  int64_t stride_h, stride_w;
+  int32_t epilogue;
+  int32_t math_mode;
+} b200_conv_desc;
+
+B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc);
+B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
+                    const float *bias, float *Y, void *workspace, size_t workspace_bytes);
+
+/* ------------------------------------------------------------------------------------------
+ * Row-wise kernels. A tensor is viewed as [outer, len, inner] around the reduced axis
+ * (inner == 1 for the last axis).
+ * ------------------------------------------------------------------------------------------ */
+/* ONNXSoftmax, single numpy axis (pure_implementations.py:346-366): max, exp(x-max), sum, div. */
+B200_API int b200_softmax_f32(void *stream, const float *x, float *y, int64_t outer, int64_t len, int64_t inner);
+/* ONNXLogSoftmax (pure_implementations.py:594-616): (x-max) - log(sum(exp(x-max))). */
+B200_API int b200_logsoftmax_f32(void *stream, const float *x, float *y, int64_t outer, int64_t len, int64_t inner);
+/* ONNXReduceMean (pure_implementations.py:97-109): np.mean over one contiguous block of axes. */
+B200_API int b200_reduce_mean_f32(void *stream, const float *x, float *y, int64_t outer, int64_t len, int64_t inner);
+/* The 9-node LayerNormalization chain ReduceMean,Sub,Pow(2),ReduceMean,Add(eps),Sqrt,Div,Mul,Add
+ * (the nodes of pure_implementations.py:97-109, :77-94, :59-74, :41-56 in that order) over the
+ * last axis: y = (x-mean)/sqrt(mean((x-mean)^2)+eps)*gamma+beta. gamma/beta may be NULL. */
+B200_API int b200_layernorm_f32(void *stream, const float *x, const float *gamma, const float *beta, float *y,
+                       int64_t rows, int64_t len, float eps);
+
+/* ------------------------------------------------------------------------------------------
+ * Elementwise nodes with numpy broadcasting (pure_implementations.py:77-94 Add/Sub/Mul/Div,
+ * :59-74 Pow). `shape` is the broadcast output shape (rank <= 8); a_strides/b_strides are element
+ * strides of each operand in that shape, 0 on broadcast axes.
+ * ------------------------------------------------------------------------------------------ */
+B200_API int b200_binary_f32(void *stream, int op, const float *a, const float *b, float *c, int rank,
+                    const int64_t *shape, const int64_t *a_strides, const int64_t *b_strides);
+/* Sqrt (:41-56), Erf (:112-127), Relu (:462-474), and the fused Gelu chain. */
+B200_API int b200_unary_f32(void *stream, int op, const float *x, float *y, int64_t numel);
+
+/* Layout helper used either side of attention: out[b,h,s,d] = in[b,s,h,d] (ONNXTranspose
+ * perm [0,2,1,3], pure_implementations.py:369-379). The same call undoes it with s,h swapped. */
+B200_API int b200_transpose_0213_f32(void *stream, const float *x, float *y, int64_t d0, int64_t d1, int64_t d2,
+                            int64_t d3);
+/* out[c,r] = in[r,c] per batch (ONNXTranspose perm [1,0], the runtime Transpose(W) before MatMul). */
+B200_API int b200_transpose_2d_f32(void *stream, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_OPS_H */

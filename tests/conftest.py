@@ -1,0 +1,36 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def lib():
+    """The built C-ABI library. Building is part of the repository's build step, not of the tests."""
+    from dace_onnx_b200 import _lib
+    return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("a test marked gpu ran without a CUDA device")
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean(request):
+    """After every GPU test: no kernel may have reported an expired wait."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None:
+        from dace_onnx_b200 import _lib
+        _lib.device_status()
