@@ -22,6 +22,18 @@ __device__ __forceinline__ float apply_epilogue(int epi, float acc, float bias, 
   }
 }
 
+// Same, with the epilogue fixed at compile time (used inside unrolled per-row loops so that the
+// choice is made once per block, not once per element).
+template <int EPI>
+__device__ __forceinline__ float apply_epilogue_t(float acc, float bias, float residual, float scale) {
+  if (EPI == B200_EPI_BIAS) return acc + bias;
+  if (EPI == B200_EPI_BIAS_RELU) return fmaxf(acc + bias, 0.f);
+  if (EPI == B200_EPI_BIAS_GELU) return gelu_erf(acc + bias);
+  if (EPI == B200_EPI_BIAS_RESIDUAL) return (acc + bias) + residual;
+  if (EPI == B200_EPI_SCALE) return acc * scale;
+  return acc;
+}
+
 int gemm_simt(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
               const float *residual, float *Y);
 int conv2d_simt(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias,

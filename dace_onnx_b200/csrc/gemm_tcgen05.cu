@@ -6,9 +6,11 @@
 //               (128B-swizzled, 32 fp32 of K per block) into a ring of shared-memory stages;
 //   warp 1      MMA issuer: allocates TMEM, one lane issues tcgen05.mma for each 8-wide k-step
 //               and commits stage release / accumulator-ready events to mbarriers;
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator (row = TMEM lane, one row per thread),
-//               apply the fused epilogue (bias / ReLU / erf-Gelu / residual / scale) and store;
-//   warps 6-9   (3xTF32 mode only) split warps: rewrite each landed stage in place as
+//   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (row = TMEM lane, one row per thread, two
+//               warps per lane quarter), apply the fused epilogue (bias / ReLU / erf-Gelu /
+//               residual / scale) and store with 256-bit vector stores, each thread writing whole
+//               32-byte sectors of its row (128-bit / scalar stores when Y is less aligned);
+//   warps 10-13 (3xTF32 mode only) split warps: rewrite each landed stage in place as
 //               hi = tf32(x) and write lo = tf32(x - hi) beside it, so that the issuer can run
 //               lo*hi + hi*lo + hi*hi into the same fp32 accumulator (fp32-accurate products).
 // Two TMEM accumulators alternate so that the epilogue of tile i overlaps the MMAs of tile i+1.
@@ -160,6 +162,7 @@ struct GemmParams {
   int64_t num_tiles;
   int batch_inner;
   int a_bi, a_bo, b_bi, b_bo;  // 1 when the operand advances with that batch index, 0 when broadcast
+  int vec;                     // widest aligned access to Y / residual rows: 8, 4 or 1 floats
   int64_t ldy, y_stride_outer, y_stride_inner;
   int epilogue;
   float scale;
@@ -171,33 +174,85 @@ struct GemmParams {
 
 // k-blocks per in-core accumulation chunk in 3xTF32 mode (2 x 32 = 64 values of K, 24 MMAs).
 constexpr int kSplitChunkKb = 2;
+constexpr int kEpilogueWarps = 8;
 
-// Epilogue + store of 32 consecutive columns [n0, n0+32) of output row m held in registers.
-__device__ __forceinline__ void store_row32(const GemmParams &p, const float *v, int64_t m, int64_t row_off,
-                                            int64_t n0, bool vec_ok) {
+__device__ __forceinline__ void ld_global_v8(const float *p, float *v) {
+  asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void st_global_v8(float *p, const float *v) {
+  asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
+}
+
+// Fused epilogue and store of 32 consecutive columns [n0, n0+32) of output row m, held in registers
+// by one thread. Each thread owns 128 contiguous bytes of its row; with 32-byte vector accesses every
+// store instruction writes whole 32-byte sectors (vec == 8), else 16-byte or scalar accesses.
+template <int EPI>
+__device__ __forceinline__ void finish_row32_t(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0) {
+  constexpr bool kBias = EPI == B200_EPI_BIAS || EPI == B200_EPI_BIAS_RELU || EPI == B200_EPI_BIAS_GELU ||
+                         EPI == B200_EPI_BIAS_RESIDUAL;
+  constexpr bool kResidual = EPI == B200_EPI_BIAS_RESIDUAL;
   if (m >= p.M || n0 >= p.N) return;
+  const bool full = n0 + 32 <= p.N;
   float *yrow = p.Y + row_off + n0;
-  const float *rrow = p.residual ? p.residual + row_off + n0 : nullptr;
-  if (vec_ok && n0 + 32 <= p.N) {
+  const float *rrow = kResidual ? p.residual + row_off + n0 : nullptr;
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), r4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (p.bias) b4 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j));
-      if (rrow) r4 = *reinterpret_cast<const float4 *>(rrow + j);
-      float4 o;
-      o.x = apply_epilogue(p.epilogue, v[j + 0], b4.x, r4.x, p.scale);
-      o.y = apply_epilogue(p.epilogue, v[j + 1], b4.y, r4.y, p.scale);
-      o.z = apply_epilogue(p.epilogue, v[j + 2], b4.z, r4.z, p.scale);
-      o.w = apply_epilogue(p.epilogue, v[j + 3], b4.w, r4.w, p.scale);
-      *reinterpret_cast<float4 *>(yrow + j) = o;
-    }
-  } else {
+  for (int j = 0; j < 32; j += 8) {
+    float b[8], r[8];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (n0 + j < p.N)
-        yrow[j] = apply_epilogue(p.epilogue, v[j], p.bias ? __ldg(p.bias + n0 + j) : 0.f, rrow ? rrow[j] : 0.f,
-                                 p.scale);
+    for (int i = 0; i < 8; ++i) b[i] = r[i] = 0.f;
+    if (kBias) {
+      if (full) {
+        const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j));
+        const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j + 4));
+        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (n0 + j + i < p.N) b[i] = __ldg(p.bias + n0 + j + i);
+      }
     }
+    if (kResidual) {
+      if (full && p.vec == 8) {
+        ld_global_v8(rrow + j, r);
+      } else if (full && p.vec == 4) {
+        const float4 r0 = *reinterpret_cast<const float4 *>(rrow + j);
+        const float4 r1 = *reinterpret_cast<const float4 *>(rrow + j + 4);
+        r[0] = r0.x; r[1] = r0.y; r[2] = r0.z; r[3] = r0.w; r[4] = r1.x; r[5] = r1.y; r[6] = r1.z; r[7] = r1.w;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (n0 + j + i < p.N) r[i] = rrow[j + i];
+      }
+    }
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = apply_epilogue_t<EPI>(v[j + i], b[i], r[i], p.scale);
+    if (full && p.vec == 8) {
+      st_global_v8(yrow + j, o);
+    } else if (full && p.vec == 4) {
+      *reinterpret_cast<float4 *>(yrow + j) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4 *>(yrow + j + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (n0 + j + i < p.N) yrow[j + i] = o[i];
+    }
+  }
+}
+
+// The epilogue kind is uniform for the launch: choose the specialised body once per 32x32 block.
+__device__ __forceinline__ void finish_row32(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0) {
+  switch (p.epilogue) {
+    case B200_EPI_BIAS: finish_row32_t<B200_EPI_BIAS>(p, v, m, row_off, n0); break;
+    case B200_EPI_BIAS_RELU: finish_row32_t<B200_EPI_BIAS_RELU>(p, v, m, row_off, n0); break;
+    case B200_EPI_BIAS_GELU: finish_row32_t<B200_EPI_BIAS_GELU>(p, v, m, row_off, n0); break;
+    case B200_EPI_BIAS_RESIDUAL: finish_row32_t<B200_EPI_BIAS_RESIDUAL>(p, v, m, row_off, n0); break;
+    case B200_EPI_SCALE: finish_row32_t<B200_EPI_SCALE>(p, v, m, row_off, n0); break;
+    default: finish_row32_t<B200_EPI_NONE>(p, v, m, row_off, n0); break;
   }
 }
 
@@ -205,10 +260,12 @@ template <int BN, bool SPLIT3>
 struct Cfg {
   static constexpr int kBStageBytes = BN * BK * 4;
   static constexpr int kStageBytes = (A_STAGE_BYTES + kBStageBytes) * (SPLIT3 ? 2 : 1);
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; BN is a power of two
-  static constexpr int kThreads = SPLIT3 ? 320 : 192;
+  static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + (SPLIT3 ? 4 : 0));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kColsPerWarp = BN / 2;  // two epilogue warps share each TMEM lane quarter
 };
 
 template <int BN, bool B_MN, bool SPLIT3>
@@ -242,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 128);
+      mbar_init(bar_tempty + 8 * a, kEpilogueWarps * 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -343,14 +400,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + kEpilogueWarps) {
     // ------------------------------- epilogue -------------------------------
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) are visible to this warp
+    // Warp w reads TMEM lanes [32*(w%4), +32); the two warps of a lane quarter split the columns.
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int col0 = (ew >> 2) * C::kColsPerWarp;
     int acc = 0;
     uint32_t acc_ph = 0;
-    const bool vec_ok = (p.ldy % 4 == 0) && (p.y_stride_outer % 4 == 0) && (p.y_stride_inner % 4 == 0) &&
-                        ((reinterpret_cast<uintptr_t>(p.Y) & 15u) == 0) &&
-                        (!p.residual || (reinterpret_cast<uintptr_t>(p.residual) & 15u) == 0);
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       const int n_t = (int)(tile % p.num_n_tiles);
@@ -361,21 +418,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int64_t m = (int64_t)m_t * BM + quarter * 32 + lane;
       const int64_t row_off = bo * p.y_stride_outer + bi * p.y_stride_inner + m * p.ldy;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      auto finish_block = [&](float *v, int c0) { finish_row32(p, v, m, row_off, (int64_t)n_t * BN + c0); };
       if (SPLIT3) {
         // Sum the per-chunk accumulators in registers, then apply the epilogue once.
-        float sum[BN];
+        float sum[C::kColsPerWarp];
 #pragma unroll
-        for (int j = 0; j < BN; ++j) sum[j] = 0.f;
+        for (int j = 0; j < C::kColsPerWarp; ++j) sum[j] = 0.f;
         for (int kb0 = 0; kb0 < p.num_kb; kb0 += kSplitChunkKb) {
           if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
           tc_fence_after();
 #pragma unroll
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c = 0; c < C::kColsPerWarp; c += 32) {
             uint32_t v[32];
-            tmem_ld32(lane_addr + (uint32_t)(acc * BN + c0), v);
+            tmem_ld32(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sum[c0 + j] += __uint_as_float(v[j]);
+            for (int j = 0; j < 32; ++j) sum[c + j] += __uint_as_float(v[j]);
           }
           tc_fence_before();
           mbar_arrive(bar_tempty + 8 * acc);
@@ -383,29 +441,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!ok) break;
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32)
-          store_row32(p, &sum[c0], m, row_off, (int64_t)n_t * BN + c0, vec_ok);
+        for (int c = 0; c < C::kColsPerWarp; c += 32) finish_block(&sum[c], col0 + c);
       } else {
         if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
         tc_fence_after();
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c = 0; c < C::kColsPerWarp; c += 32) {
           uint32_t v[32];
           float f[32];
-          tmem_ld32(lane_addr + (uint32_t)(acc * BN + c0), v);
+          tmem_ld32(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
           tmem_ld_wait();
+          if (c + 32 >= C::kColsPerWarp) {
+            // last read of this accumulator by this thread: hand it back before the stores
+            tc_fence_before();
+            mbar_arrive(bar_tempty + 8 * acc);
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          store_row32(p, f, m, row_off, (int64_t)n_t * BN + c0, vec_ok);
+          finish_block(f, col0 + c);
         }
-        tc_fence_before();
-        mbar_arrive(bar_tempty + 8 * acc);  // 128 arrivals release the accumulator
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
     }
   } else if (SPLIT3) {
     // ------------------------------- 3xTF32 split warps -------------------------------
-    const int t = threadIdx.x - 192;  // 0..127
+    const int t = threadIdx.x - 32 * C::kSplitWarp0;  // 0..127
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -591,6 +651,13 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
                             d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
       return rc;
   }
+  // Widest access that every output (and residual) row segment is aligned for.
+  auto aligned_to = [&](int elems) {
+    const uintptr_t mask = (uintptr_t)elems * 4 - 1;
+    return (reinterpret_cast<uintptr_t>(Y) & mask) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & mask) == 0) &&
+           d.ldy % elems == 0 && d.y_stride_inner % elems == 0 && d.y_stride_outer % elems == 0;
+  };
+  p.vec = aligned_to(8) ? 8 : aligned_to(4) ? 4 : 1;
   p.M = d.M;
   p.N = d.N;
   p.num_kb = (int)((d.K + BK - 1) / BK);

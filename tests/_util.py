@@ -11,8 +11,8 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 RTOL, ATOL = 1e-4, 1e-5
 # The reference's own comparator (daceml/testing/utils.py:6).
 REF_RTOL, REF_ATOL = 1e-5, 1e-4
-# Single-pass TF32: 10-bit mantissa operands, stated wider tolerance.
-TF32_RTOL, TF32_ATOL = 2e-2, 2e-3
+# Single-pass TF32: operands cut to a 10-bit mantissa by the tensor core; stated wider tolerance.
+TF32_RTOL, TF32_ATOL = 2e-2, 1e-2
 
 
 def golden(name):
