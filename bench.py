@@ -235,11 +235,21 @@ def run_b200(args, wl):
     for kind in ops_report:
         ops_report[kind]["share"] = per_kind[kind][0] / total_sec
     g = per_kind.get("gemm", [1.0, 0.0, 0.0, 1])
+    # DRAM traffic of the dense GEMM kernel: ncu measured dram read+write = 0.83 x the algorithmic bytes
+    # 4(MK+NK+MN) on the captured small case (profiles/gemm_tc_tf32_qkv_16384x3072x1024.txt: 232.7 MB vs
+    # 281.0 MB; part of the output is still in L2 when the kernel ends). Traffic grows in proportion to M,
+    # so the per-launch figure here is that ratio times the average algorithmic bytes of a bench launch.
+    t_tok = (batch // world if batch % world == 0 else local) and min(args.micro_batch, local) * seq
+    gemm_shapes = [(3 * hidden, hidden), (hidden, hidden), (ffn, hidden), (hidden, ffn)]
+    alg_bytes = sum(4 * (t_tok * k + n * k + t_tok * n) for n, k in gemm_shapes) / len(gemm_shapes)
+    traffic = 0.83 * alg_bytes
     achieved = g[1] / g[0] / 1e12
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, K-major, TF32> (dense projections)",
                 "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                 "peak_source": "%s bf16 sustained / 2 (TF32 runs at half the bf16 rate)" % peaks["source"],
-                "avg_launch_ms": g[0] * 1e3 / max(g[3], 1), "traffic": None}
+                "avg_launch_ms": g[0] * 1e3 / max(g[3], 1), "traffic": traffic,
+                "traffic_unit": "bytes per launch (scaled from an ncu capture of a smaller launch)",
+                "algorithmic_bytes": alg_bytes}
 
     line = None
     if rank == 0:
