@@ -239,7 +239,7 @@ def run_b200(args, wl):
     # 4(MK+NK+MN) on the captured small case (profiles/gemm_tc_tf32_qkv_16384x3072x1024.txt: 232.7 MB vs
     # 281.0 MB; part of the output is still in L2 when the kernel ends). Traffic grows in proportion to M,
     # so the per-launch figure here is that ratio times the average algorithmic bytes of a bench launch.
-    t_tok = (batch // world if batch % world == 0 else local) and min(args.micro_batch, local) * seq
+    t_tok = min(args.micro_batch, local) * seq
     gemm_shapes = [(3 * hidden, hidden), (hidden, hidden), (ffn, hidden), (hidden, ffn)]
     alg_bytes = sum(4 * (t_tok * k + n * k + t_tok * n) for n, k in gemm_shapes) / len(gemm_shapes)
     traffic = 0.83 * alg_bytes
@@ -334,7 +334,20 @@ def kernel_cases(device):
             return fn, 2 * b * h * s * s * d, 4 * (2 * b * s * hid + b * h * s * s), "hbm"
         return make
 
+    def conv(n, c, hw, m, mode):
+        def make():
+            x = torch.rand(n, c, hw, hw, device=device, generator=g)
+            bound = 1.0 / (c * 9) ** 0.5
+            w = (torch.rand(m, c, 3, 3, device=device, generator=g) * 2 - 1) * bound
+            b = (torch.rand(m, device=device, generator=g) * 2 - 1) * bound
+            y = torch.empty(n, m, hw, hw, device=device)
+            ws = torch.empty(2 * x.numel() * 4 + (1 << 20), device=device, dtype=torch.uint8)
+            fn = lambda: ops.conv2d(x, w, b, out=y, pads=(1, 1, 1, 1), relu=True, workspace=ws, math_mode=mode)  # noqa
+            return fn, 2 * n * hw * hw * m * c * 9, 4 * (x.numel() + y.numel()), "tensor"
+        return make
+
     return {
+        "conv_c2_fp32x3": conv(256, 64, 56, 64, "fp32x3"), "conv_c2_tf32": conv(256, 64, 56, 64, "tf32"),
         "softmax_c4": softmax_c4, "layernorm_c4": layernorm_c4,
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),
         "gemm_tf32_ffn2": gemm(16384, 1024, 4096, "tf32"), "gemm_tf32_proj": gemm(16384, 1024, 1024, "tf32"),

@@ -112,15 +112,15 @@ static bool conv_out_shape(const b200_conv_desc &d, int64_t *oh, int64_t *ow) {
 }
 
 extern "C" B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc) {
-  (void)desc;
-  return 0;
+  if (!desc) return 0;
+  // alignment of X is unknown here; the tensor-core path needs this much whenever the shape allows it
+  static const float *const kAligned = nullptr;
+  return conv2d_tc_supported(*desc, kAligned) ? conv2d_tc_workspace_bytes(*desc) : 0;
 }
 
 extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
                                const float *bias, float *Y, void *workspace, size_t workspace_bytes) {
   cudaStream_t st = (cudaStream_t)stream;
-  (void)workspace;
-  (void)workspace_bytes;
   if (!desc) return fail(B200_EINVAL, "conv: null descriptor");
   b200_conv_desc d = *desc;
   if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.M < 0) return fail(B200_EINVAL, "conv: bad extent");
@@ -132,5 +132,10 @@ extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc
     return fail(B200_EINVAL, "conv: unsupported epilogue %d", d.epilogue);
   if (d.epilogue != B200_EPI_NONE && !bias) return fail(B200_EINVAL, "conv: epilogue %d needs a bias", d.epilogue);
   if (d.epilogue == B200_EPI_NONE) bias = nullptr;
+  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
+    return fail(B200_EINVAL, "conv: unknown math mode %d", d.math_mode);
+  // Tensor-core implicit GEMM when TMA can address the NHWC copy; the CUDA-core kernel otherwise
+  // (strided convolutions, channel counts that are not multiples of 4, plain fp32 arithmetic).
+  if (conv2d_tc_supported(d, X)) return conv2d_tc(st, d, X, W, bias, Y, OH, OW, workspace, workspace_bytes);
   return conv2d_simt(st, d, X, W, bias, Y, OH, OW);
 }

@@ -45,4 +45,14 @@ bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, 
 int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
             const float *residual, float *Y);
 
+// Tensor-core convolution: NCHW -> NHWC and filter repack into the caller's workspace, then the
+// implicit GEMM. Supported for stride 1 and channel counts that are multiples of 4 (>= 16).
+bool conv2d_tc_supported(const b200_conv_desc &d, const float *X);
+size_t conv2d_tc_workspace_bytes(const b200_conv_desc &d);
+int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias, float *Y,
+              int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes);
+
+// out[b][c][r] = in[b][r][c]
+int transpose_2d(cudaStream_t st, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols);
+
 }  // namespace b200

@@ -204,6 +204,14 @@ int launch_unary(cudaStream_t st, const float *x, float *y, int64_t numel) {
 }
 
 }  // namespace
+
+int transpose_2d(cudaStream_t st, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols) {
+  if (batch > 65535 || (rows + 31) / 32 > 65535) return fail(B200_EUNSUPPORTED, "transpose: extent too large");
+  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), (unsigned)batch);
+  transpose_2d_kernel<<<grid, 256, 0, st>>>(x, y, rows, cols);
+  return check_launch("transpose_2d");
+}
+
 }  // namespace b200
 
 using namespace b200;

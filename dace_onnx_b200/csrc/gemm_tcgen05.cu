@@ -155,7 +155,18 @@ __device__ __forceinline__ float to_tf32_rna(float x) {
   return __uint_as_float(u);
 }
 
+// Geometry of a stride-1 convolution run as an implicit GEMM: rows of the GEMM are output pixels,
+// grouped in 8x8 blocks (two blocks per 128-row tile); K runs over (kh, kw, 32-channel block).
+struct ConvGeom {
+  int KW, pad_h, pad_w;
+  int OH, OW;
+  int blocks_w, blocks_per_img;  // 8x8 output blocks per row / per image
+  int cblocks;                   // 32-channel blocks per filter tap
+  int64_t total_blocks;          // images * blocks_per_img
+};
+
 struct GemmParams {
+  ConvGeom cv;
   int64_t M, N;
   int num_kb;
   int num_m_tiles, num_n_tiles;
@@ -256,6 +267,32 @@ __device__ __forceinline__ void finish_row32(const GemmParams &p, float *v, int6
   }
 }
 
+// Convolution epilogue for 32 output channels [n0, n0+32) of one output pixel: bias / ReLU, then
+// NCHW stores. For a fixed channel the 32 lanes of a warp hold 4 rows x 8 consecutive pixels, i.e.
+// four whole 32-byte sectors per store instruction.
+template <int EPI>
+__device__ __forceinline__ void finish_pixel32_t(const GemmParams &p, const float *v, int64_t pix_off,
+                                                 int64_t chan_stride, int64_t n0) {
+  float *y = p.Y + pix_off + n0 * chan_stride;
+  const bool full = n0 + 32 <= p.N;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    if (full || n0 + j < p.N) {
+      const float b = (EPI != B200_EPI_NONE) ? __ldg(p.bias + n0 + j) : 0.f;
+      y[j * chan_stride] = apply_epilogue_t<EPI>(v[j], b, 0.f, 1.f);
+    }
+  }
+}
+__device__ __forceinline__ void finish_pixel32(const GemmParams &p, const float *v, bool valid, int64_t pix_off,
+                                               int64_t chan_stride, int64_t n0) {
+  if (!valid || n0 >= p.N) return;
+  switch (p.epilogue) {
+    case B200_EPI_BIAS: finish_pixel32_t<B200_EPI_BIAS>(p, v, pix_off, chan_stride, n0); break;
+    case B200_EPI_BIAS_RELU: finish_pixel32_t<B200_EPI_BIAS_RELU>(p, v, pix_off, chan_stride, n0); break;
+    default: finish_pixel32_t<B200_EPI_NONE>(p, v, pix_off, chan_stride, n0); break;
+  }
+}
+
 template <int BN, bool SPLIT3>
 struct Cfg {
   static constexpr int kBStageBytes = BN * BK * 4;
@@ -268,7 +305,7 @@ struct Cfg {
   static constexpr int kColsPerWarp = BN / 2;  // two epilogue warps share each TMEM lane quarter
 };
 
-template <int BN, bool B_MN, bool SPLIT3>
+template <int BN, bool B_MN, bool SPLIT3, bool CONV>
 __global__ void __launch_bounds__(Cfg<BN, SPLIT3>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
@@ -329,11 +366,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int m_t = (int)(r % p.num_m_tiles);
         const int64_t batch = r / p.num_m_tiles;
         const int bo = (int)(batch / p.batch_inner), bi = (int)(batch % p.batch_inner);
+        // convolution: the two 8x8 output blocks of this tile, decomposed once per tile (integer
+        // division is slow and this thread is alone on the critical path of every load)
+        int cv_img[2] = {0, 0}, cv_x[2] = {0, 0}, cv_y[2] = {0, 0};
+        if (CONV) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int64_t blk = 2 * (int64_t)m_t + h;
+            cv_img[h] = (int)(blk / p.cv.blocks_per_img);
+            const int rem = (int)(blk - (int64_t)cv_img[h] * p.cv.blocks_per_img);
+            const int by = rem / p.cv.blocks_w;
+            cv_y[h] = by * 8 - p.cv.pad_h;
+            cv_x[h] = (rem - by * p.cv.blocks_w) * 8 - p.cv.pad_w;
+          }
+        }
+        int cv_kh = 0, cv_kw = 0, cv_cb = 0;  // filter tap and channel block of the current k-block
         bool ok = true;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
           mbar_expect_tx(bar_full + 8 * s, A_STAGE_BYTES + C::kBStageBytes);
-          tma_load_4d(stage_a(s), &map_a, bar_full + 8 * s, kb * BK, m_t * BM, bi * p.a_bi, bo * p.a_bo);
+          if (CONV) {
+            // The A rows are the input pixels under tap (kh, kw) for the two output blocks.
+            // Coordinates left of / above the image (the zero padding) and blocks past the last
+            // image are filled with zeros by the TMA unit.
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              tma_load_4d(stage_a(s) + h * (A_STAGE_BYTES / 2), &map_a, bar_full + 8 * s, cv_cb * BK, cv_x[h] + cv_kw,
+                          cv_y[h] + cv_kh, cv_img[h]);
+            if (++cv_cb == p.cv.cblocks) {
+              cv_cb = 0;
+              if (++cv_kw == p.cv.KW) { cv_kw = 0; ++cv_kh; }
+            }
+          } else {
+            tma_load_4d(stage_a(s), &map_a, bar_full + 8 * s, kb * BK, m_t * BM, bi * p.a_bi, bo * p.a_bo);
+          }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j)
@@ -418,7 +484,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int64_t m = (int64_t)m_t * BM + quarter * 32 + lane;
       const int64_t row_off = bo * p.y_stride_outer + bi * p.y_stride_inner + m * p.ldy;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      auto finish_block = [&](float *v, int c0) { finish_row32(p, v, m, row_off, (int64_t)n_t * BN + c0); };
+      // convolution: this thread's row is one output pixel of one of the tile's two 8x8 blocks
+      bool cv_valid = false;
+      int64_t cv_off = 0, cv_cs = 0;
+      if (CONV) {
+        const int row = quarter * 32 + lane;
+        const int64_t blk = 2 * (int64_t)m_t + (row >> 6);
+        const int img = (int)(blk / p.cv.blocks_per_img);
+        const int rem = (int)(blk - (int64_t)img * p.cv.blocks_per_img);
+        const int by = rem / p.cv.blocks_w, bx = rem - by * p.cv.blocks_w;
+        const int oh = by * 8 + ((row & 63) >> 3), ow = bx * 8 + (row & 7);
+        cv_valid = blk < p.cv.total_blocks && oh < p.cv.OH && ow < p.cv.OW;
+        cv_cs = (int64_t)p.cv.OH * p.cv.OW;
+        cv_off = (int64_t)img * p.N * cv_cs + (int64_t)oh * p.cv.OW + ow;
+      }
+      auto finish_block = [&](float *v, int c0) {
+        if (CONV) finish_pixel32(p, v, cv_valid, cv_off, cv_cs, (int64_t)n_t * BN + c0);
+        else finish_row32(p, v, m, row_off, (int64_t)n_t * BN + c0);
+      };
       if (SPLIT3) {
         // Sum the per-chunk accumulators in registers, then apply the epilogue once.
         float sum[C::kColsPerWarp];
@@ -532,12 +615,12 @@ EncodeTiledFn get_encode_fn() {
 
 // rank-4 fp32 map: dims {d0 (contiguous), d1, d2, d3}, byte strides for d1..d3, zero OOB fill.
 int encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-               uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle) {
+               uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, uint32_t box2 = 1) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
   cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
-  cuuint32_t box[4] = {box0, box1, 1, 1};
+  cuuint32_t box[4] = {box0, box1, box2, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), gdim, gstr, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -566,10 +649,10 @@ void batch_axis(int64_t extent, int64_t stride_elems, uint64_t fallback_bytes, u
   }
 }
 
-template <int BN, bool B_MN, bool SPLIT3>
+template <int BN, bool B_MN, bool SPLIT3, bool CONV = false>
 int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   using C = Cfg<BN, SPLIT3>;
-  auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3>;
+  auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3, CONV>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
     return fail(B200_ECUDA, "gemm(tc): cannot set dynamic shared memory to %d", C::kSmemBytes);
   const int64_t grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
@@ -587,6 +670,33 @@ int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtensorMap 
   }
   return fail(B200_EINVAL, "gemm(tc): no kernel for BN=%d", bn);
 }
+
+// OIHW filter -> [Cout][KH*KW][Cp] with the channel axis zero-padded to Cp (a multiple of 32): the
+// K order (tap, channel) in which the implicit GEMM walks the input.
+__global__ void __launch_bounds__(256)
+conv_repack_filter_kernel(const float *__restrict__ w, float *__restrict__ out, int64_t M, int C, int taps, int Cp) {
+  const int64_t total = M * taps * Cp;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Cp);
+    const int64_t r = i / Cp;
+    const int tap = (int)(r % taps);
+    const int64_t m = r / taps;
+    out[i] = c < C ? w[(m * C + c) * taps + tap] : 0.f;
+  }
+}
+
+template <bool SPLIT3>
+int launch_conv_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
+  switch (bn) {
+    case 64: return launch_cfg<64, false, SPLIT3, true>(st, ma, mb, p);
+    case 128: return launch_cfg<128, false, SPLIT3, true>(st, ma, mb, p);
+    case 256:
+      if constexpr (!SPLIT3) return launch_cfg<256, false, false, true>(st, ma, mb, p);
+  }
+  return fail(B200_EINVAL, "conv(tc): no kernel for BN=%d", bn);
+}
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 int pick_bn(int64_t N, bool split3) {
   const int cands[3] = {256, 128, 64};
@@ -625,7 +735,7 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   const int bn = pick_bn(d.N, split3);
 
   CUtensorMap ma, mb;
-  GemmParams p;
+  GemmParams p{};
   {
     uint64_t dims[4] = {(uint64_t)d.K, (uint64_t)d.M, 1, 1};
     uint64_t str[3] = {(uint64_t)d.lda * 4, 0, 0};
@@ -680,6 +790,92 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
     return split3 ? launch_bn<false, true>(st, bn, ma, mb, p) : launch_bn<false, false>(st, bn, ma, mb, p);
   }
   return split3 ? launch_bn<true, true>(st, bn, ma, mb, p) : launch_bn<true, false>(st, bn, ma, mb, p);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Convolution on the tensor cores (stride 1, any symmetric zero padding, any filter size)
+// ---------------------------------------------------------------------------------------------
+bool conv2d_tc_supported(const b200_conv_desc &d, const float *X) {
+  if (d.math_mode == B200_MATH_FP32) return false;
+  if (d.stride_h != 1 || d.stride_w != 1) return false;
+  if (d.C % 4 != 0 || d.C < 16) return false;  // TMA: pixel stride C*4 bytes must be a multiple of 16
+  if (!aligned16(X)) return false;
+  if (d.N > 0x7fffffffLL || d.H > 0x7fffffffLL || d.W > 0x7fffffffLL || d.M > 0x7fffffffLL) return false;
+  if (d.KH * d.KW * ((d.C + 31) / 32) > 0x7fffffffLL) return false;
+  return true;
+}
+
+size_t conv2d_tc_workspace_bytes(const b200_conv_desc &d) {
+  const size_t x_t = align256((size_t)d.N * d.H * d.W * d.C * 4);
+  const size_t w_t = align256((size_t)d.M * d.KH * d.KW * ((d.C + 31) / 32 * 32) * 4);
+  return x_t + w_t;
+}
+
+int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias, float *Y,
+              int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes) {
+  if (workspace_bytes < conv2d_tc_workspace_bytes(d) || !workspace)
+    return fail(B200_EWORKSPACE, "conv: workspace of %zu bytes needed, %zu given", conv2d_tc_workspace_bytes(d),
+                workspace_bytes);
+  if (!aligned16(workspace)) return fail(B200_EINVAL, "conv: workspace must be 16-byte aligned");
+  const int Cp = (int)((d.C + 31) / 32 * 32);
+  const int taps = (int)(d.KH * d.KW);
+  float *xt = static_cast<float *>(workspace);
+  float *wt = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)d.N * d.H * d.W * d.C * 4));
+
+  // 1. X: NCHW -> NHWC (per image a [C, H*W] -> [H*W, C] transpose), so that the 32 channels of a
+  //    k-block are contiguous and filter-tap shifts move only the outer TMA coordinates.
+  if (int rc = transpose_2d(st, X, xt, d.N, d.C, d.H * d.W)) return rc;
+  // 2. filter repack
+  {
+    const int64_t total = d.M * taps * Cp;
+    int64_t g = (total + 255) / 256;
+    if (g > kNumSMs * 8) g = kNumSMs * 8;
+    conv_repack_filter_kernel<<<(unsigned)g, 256, 0, st>>>(W, wt, d.M, (int)d.C, taps, Cp);
+    if (int rc = check_launch("conv_repack_filter")) return rc;
+  }
+  // 3. implicit GEMM
+  const bool split3 = d.math_mode == B200_MATH_FP32X3;
+  const int bn = pick_bn(d.M, split3);
+  CUtensorMap ma, mb;
+  {
+    uint64_t dims[4] = {(uint64_t)d.C, (uint64_t)d.W, (uint64_t)d.H, (uint64_t)d.N};
+    uint64_t str[3] = {(uint64_t)d.C * 4, (uint64_t)d.W * d.C * 4, (uint64_t)d.H * d.W * d.C * 4};
+    if (int rc = encode_map(&ma, xt, dims, str, BK, 8, CU_TENSOR_MAP_SWIZZLE_128B, 8)) return rc;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)taps * Cp, (uint64_t)d.M, 1, 1};
+    uint64_t str[3] = {(uint64_t)taps * Cp * 4, (uint64_t)taps * Cp * 4 * d.M, (uint64_t)taps * Cp * 4 * d.M};
+    if (int rc = encode_map(&mb, wt, dims, str, BK, (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
+  }
+  GemmParams p{};
+  p.cv.KW = (int)d.KW;
+  p.cv.pad_h = (int)d.pad_h;
+  p.cv.pad_w = (int)d.pad_w;
+  p.cv.OH = (int)OH;
+  p.cv.OW = (int)OW;
+  p.cv.blocks_w = (int)((OW + 7) / 8);
+  p.cv.blocks_per_img = p.cv.blocks_w * (int)((OH + 7) / 8);
+  p.cv.cblocks = Cp / 32;
+  p.cv.total_blocks = d.N * p.cv.blocks_per_img;
+  const int64_t m_tiles = (p.cv.total_blocks + 1) / 2;
+  if (m_tiles > 0x7fffffffLL) return fail(B200_EUNSUPPORTED, "conv: too many output tiles");
+  p.M = m_tiles * BM;
+  p.N = d.M;
+  p.num_kb = taps * p.cv.cblocks;
+  p.num_m_tiles = (int)m_tiles;
+  p.num_n_tiles = (int)((d.M + bn - 1) / bn);
+  p.batch_inner = 1;
+  p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
+  p.b_bi = p.b_bo = p.a_bi = p.a_bo = 0;
+  p.vec = 1;
+  p.epilogue = d.epilogue;
+  p.scale = 1.f;
+  p.bias = bias;
+  p.residual = nullptr;
+  p.Y = Y;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(B200_ECUDA, "conv(tc): device status word unavailable");
+  return split3 ? launch_conv_bn<true>(st, bn, ma, mb, p) : launch_conv_bn<false>(st, bn, ma, mb, p);
 }
 
 }  // namespace b200
