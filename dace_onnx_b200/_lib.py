@@ -49,6 +49,8 @@ SIGNATURES = {
     "b200_conv2d_workspace_bytes": (c_size_t, [POINTER(ConvDesc)]),
     "b200_conv2d_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_size_t]),
+    "b200_conv2d_static_scratch_bytes": (c_size_t, []),
+    "b200_conv2d_static_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_softmax_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "b200_logsoftmax_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "b200_reduce_mean_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),

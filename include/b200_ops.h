@@ -118,6 +118,23 @@ B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc);
 B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
                     const float *bias, float *Y, void *workspace, size_t workspace_bytes);
 
+/* Convolution for callers that cannot allocate device memory. No counterpart in the reference:
+ * every GPU library call there gets its workspace from an SDFG init hook (cudaMalloc in
+ * cudnn_implementations.py:281-297), which some embedders do not have -- generated code that owns
+ * nothing but its argument pointers, or a service whose device memory is fixed at start-up.
+ * Same arguments and results as b200_conv2d_f32 minus the workspace: the scratch is a fixed array of
+ * B200_CONV_STATIC_SCRATCH_BYTES inside the library, resident on every GPU that loads the library
+ * until the process exits. A convolution needing more scratch than that (see
+ * b200_conv2d_workspace_bytes) is refused with B200_EWORKSPACE. The call itself allocates and frees
+ * nothing. The first call on each device looks the array's address up (one cudaGetSymbolAddress,
+ * cached per device); make that first call with the device current and before any stream capture
+ * begins. All calls on a device share the array: calls that can overlap on the GPU (other streams or
+ * threads) race; serialise them. Contents left by earlier calls never influence a result. */
+#define B200_CONV_STATIC_SCRATCH_BYTES (32u << 20)
+B200_API size_t b200_conv2d_static_scratch_bytes(void);
+B200_API int b200_conv2d_static_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
+                           const float *bias, float *Y);
+
 /* ------------------------------------------------------------------------------------------
  * Row-wise kernels. A tensor is viewed as [outer, len, inner] around the reduced axis
  * (inner == 1 for the last axis).
