@@ -334,6 +334,16 @@ def kernel_cases(device):
             return fn, 2 * b * h * s * s * d, 4 * (2 * b * s * hid + b * h * s * s), "hbm"
         return make
 
+    def attn_fused(b, h, s, d):
+        def make():
+            qkv = rn(b, s, 3 * h * d)
+            ctx = torch.empty(b, s, h * d, device=device)
+            v4 = qkv.view(b, s, 3 * h, d)
+            fn = lambda: ops.attention_views(v4[:, :, :h], v4[:, :, h:2 * h], v4[:, :, 2 * h:], ctx.view(b, s, h, d),  # noqa
+                                             0.125, math_mode="tf32")
+            return fn, 4 * b * h * s * s * d, 16 * b * s * h * d, "tensor"
+        return make
+
     def conv(n, c, hw, m, mode):
         def make():
             x = torch.rand(n, c, hw, hw, device=device, generator=g)
@@ -353,6 +363,7 @@ def kernel_cases(device):
         "gemm_tf32_ffn2": gemm(16384, 1024, 4096, "tf32"), "gemm_tf32_proj": gemm(16384, 1024, 1024, "tf32"),
         "gemm_fp32x3_ffn1": gemm(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU), "gemm_fp32x3_proj": gemm(16384, 768, 768, "fp32x3"),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
+        "attention_fused_tf32": attn_fused(32, 16, 384, 64),
     }
 
 

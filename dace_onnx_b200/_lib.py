@@ -34,6 +34,12 @@ class GemmDesc(Structure):
         ("trans_b", c_int32), ("epilogue", c_int32), ("scale", c_float), ("math_mode", c_int32)]
 
 
+class AttentionDesc(Structure):
+    _fields_ = [(n, c_int64) for n in (
+        "batch", "heads", "seq", "head_dim", "q_row", "q_head", "q_batch", "k_row", "k_head", "k_batch",
+        "v_row", "v_head", "v_batch", "o_row", "o_head", "o_batch")] + [("scale", c_float), ("math_mode", c_int32)]
+
+
 class ConvDesc(Structure):
     _fields_ = [(n, c_int64) for n in (
         "N", "C", "H", "W", "M", "KH", "KW", "pad_h", "pad_w", "stride_h", "stride_w")] + [
@@ -46,6 +52,8 @@ SIGNATURES = {
     "b200_last_error_string": (c_char_p, []),
     "b200_device_status": (c_int, []),
     "b200_gemm_f32": (c_int, [c_void_p, POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_attention_supported": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200_attention_f32": (c_int, [c_void_p, POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_conv2d_workspace_bytes": (c_size_t, [POINTER(ConvDesc)]),
     "b200_conv2d_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_size_t]),

@@ -102,6 +102,26 @@ extern "C" B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, 
   return gemm_simt(st, d, A, B, bias, residual, Y);
 }
 
+extern "C" B200_API int b200_attention_supported(const b200_attention_desc *desc, const float *Q, const float *K,
+                                                 const float *V, const float *out) {
+  return desc && Q && K && V && out && desc->scale > 0.f && attention_tc_supported(*desc, Q, K, V, out) ? 1 : 0;
+}
+
+extern "C" B200_API int b200_attention_f32(void *stream, const b200_attention_desc *desc, const float *Q,
+                                           const float *K, const float *V, float *out) {
+  if (!desc) return fail(B200_EINVAL, "attention: null descriptor");
+  if (desc->batch < 0 || desc->heads < 0 || desc->seq < 0 || desc->head_dim < 1)
+    return fail(B200_EINVAL, "attention: negative extent");
+  if (desc->batch == 0 || desc->heads == 0 || desc->seq == 0) return B200_OK;
+  if (!Q || !K || !V || !out) return fail(B200_EINVAL, "attention: null pointer");
+  if (!b200_attention_supported(desc, Q, K, V, out))
+    return fail(B200_EUNSUPPORTED,
+                "attention: fused kernel needs TF32 mode, head_dim 64, seq %% 32 == 0 and <= 384, aligned strides "
+                "(got mode %d, head_dim %lld, seq %lld); run the unfused nodes instead",
+                desc->math_mode, (long long)desc->head_dim, (long long)desc->seq);
+  return attention_tc((cudaStream_t)stream, *desc, Q, K, V, out);
+}
+
 static bool conv_out_shape(const b200_conv_desc &d, int64_t *oh, int64_t *ow) {
   if (d.stride_h < 1 || d.stride_w < 1 || d.KH < 1 || d.KW < 1 || d.pad_h < 0 || d.pad_w < 0) return false;
   const int64_t eh = d.H + 2 * d.pad_h - d.KH, ew = d.W + 2 * d.pad_w - d.KW;

@@ -52,6 +52,11 @@ size_t conv2d_tc_workspace_bytes(const b200_conv_desc &d);
 int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias, float *Y,
               int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes);
 
+bool attention_tc_supported(const b200_attention_desc &d, const float *Q, const float *K, const float *V,
+                            const float *out);
+int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, const float *K, const float *V,
+                 float *out);
+
 // out[b][c][r] = in[b][r][c]
 int transpose_2d(cudaStream_t st, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols);
 

@@ -21,140 +21,16 @@
 
 #include "common.cuh"
 #include "contract.cuh"
+#include "tc_common.cuh"
 
 namespace b200 {
+using namespace tc;
 namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 32;                       // fp32 elements per k-block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;                    // K of one kind::tf32 instruction
 constexpr int A_STAGE_BYTES = BM * BK * 4;   // 16 KiB
-constexpr long long kWaitCycleBudget = 4000000000LL;  // ~2 s at 1.9 GHz
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait. Returns false when the CTA is aborting (budget exceeded here or in another role).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned *status, unsigned code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xffu) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycleBudget) {
-        *abort_flag = 1;
-        atomicOr(status, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
-                                            int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
-      "%6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-      "%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, descriptor version 1 (sm_100).
-//   K-major operand: rows of 32 fp32 = 128 B, 16-byte chunks XOR-swizzled with the row index
-//     (layout type 2, SWIZZLE_128B); 8-row groups 1024 B apart: LBO unused (=16 B), SBO = 1024 B.
-//   MN-major 32-bit operand: 32-wide column chunks, each [k][128 B], chunks `lbo` bytes apart. The
-//     only layout the tensor core accepts for it swizzles 32-byte chunks with (k mod 4)
-//     (layout type 1, SWIZZLE_128B_BASE32B; TMA writes it with SWIZZLE_128B_ATOM_32B), so the
-//     repeating group along K is 4 rows = 512 B: SBO = 512 B.
-constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                                   uint32_t layout_type) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version
-  d |= (uint64_t)layout_type << 61;
-  return d;
-}
-
-// Instruction descriptor for kind::tf32: fp32 accumulate, TF32 A and B, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(int n, bool b_mn_major) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
-         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
-
-__device__ __forceinline__ float to_tf32_rna(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
-}
-
 // Geometry of a stride-1 convolution run as an implicit GEMM: rows of the GEMM are output pixels,
 // grouped in 8x8 blocks (two blocks per 128-row tile); K runs over (kh, kw, 32-channel block).
 struct ConvGeom {
@@ -596,44 +472,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------------------------------------
 // Host side: tensor-map encoding and launch
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;  // process-wide driver entry point; identical for every device
-  if (!fn) {
-    void *ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// rank-4 fp32 map: dims {d0 (contiguous), d1, d2, d3}, byte strides for d1..d3, zero OOB fill.
-int encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-               uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, uint32_t box2 = 1) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
-  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
-  cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
-  cuuint32_t box[4] = {box0, box1, box2, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), gdim, gstr, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return fail(B200_ECUDA,
-                "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} strides {%llu,%llu,%llu} box {%u,%u}",
-                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
-                (unsigned long long)dims[3], (unsigned long long)strides_bytes[0],
-                (unsigned long long)strides_bytes[1], (unsigned long long)strides_bytes[2], box0, box1);
-  return B200_OK;
-}
-
 // A batch axis that is broadcast (stride 0) or trivial (extent 1) is encoded with extent 1 and a
 // valid dummy stride; the kernel then always passes coordinate 0 on it.
 void batch_axis(int64_t extent, int64_t stride_elems, uint64_t fallback_bytes, uint64_t *dim, uint64_t *stride_bytes,
@@ -713,6 +551,44 @@ int pick_bn(int64_t N, bool split3) {
 }
 
 }  // namespace
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;  // process-wide driver entry point; identical for every device
+  if (!fn) {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+int tc::encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+               uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, uint32_t box2) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t box[4] = {box0, box1, box2, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200_ECUDA,
+                "cuTensorMapEncodeTiled failed (%d): dims {%llu,%llu,%llu,%llu} strides {%llu,%llu,%llu} box {%u,%u}",
+                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                (unsigned long long)dims[3], (unsigned long long)strides_bytes[0],
+                (unsigned long long)strides_bytes[1], (unsigned long long)strides_bytes[2], box0, box1);
+  return B200_OK;
+}
+
 
 bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, const float *Y) {
   auto ok4 = [](int64_t v) { return v % 4 == 0; };

@@ -8,6 +8,8 @@ the contraction epilogues where the graph allows it:
     MatMul(x, Transpose(W)) + Add(bias)                      -> gemm, trans_b, EPI_BIAS
     ... + Add(residual)                                      -> EPI_BIAS_RESIDUAL
     ... + Div/Erf/Add/Mul/Mul (Gelu)                         -> EPI_BIAS_GELU
+    MatMul(q, k^T), Mul(1/sqrt(d)), Softmax, MatMul(p, v)    -> one fused attention kernel (TF32 mode,
+                                                                head_dim 64, seq <= 384); otherwise:
     MatMul(q, k^T) + Mul(1/sqrt(d))                          -> batched gemm, EPI_SCALE
     Reshape/Transpose [0,2,1,3] either side of attention     -> strided batch addressing (no copy)
     ReduceMean..Add (9 nodes)                                -> layernorm
@@ -31,12 +33,14 @@ class BertEncoderB200:
     of `micro_batch` sequences so that the materialised [b, heads, S, S] score tensor stays bounded.
     """
 
-    def __init__(self, layers, heads, eps=1e-12, device="cuda:0", math_mode="fp32x3", micro_batch=128):
+    def __init__(self, layers, heads, eps=1e-12, device="cuda:0", math_mode="fp32x3", micro_batch=128,
+                 fused_attention=True):
         self.device = torch.device(device)
         self.heads = heads
         self.eps = float(eps)
         self.math_mode = math_mode
         self.micro_batch = int(micro_batch)
+        self.fused_attention = bool(fused_attention)
         self.hidden = layers[0]["wq"].shape[0]
         self.ffn = layers[0]["wi"].shape[0]
         if self.hidden % heads:
@@ -62,20 +66,33 @@ class BertEncoderB200:
         if self._buf_key != key:
             h, f, nh = self.hidden, self.ffn, self.heads
             e = lambda *s: torch.empty(s, device=self.device, dtype=torch.float32)  # noqa: E731
-            self._buf = dict(qkv=e(mb, seq, 3 * h), scores=e(mb, nh, seq, seq), probs=e(mb, nh, seq, seq),
-                             ctx=e(mb, seq, h), attn=e(mb, seq, h), h1=e(mb, seq, h), inter=e(mb, seq, f),
-                             out=e(mb, seq, h), ping=e(mb, seq, h), pong=e(mb, seq, h))
+            self._buf = dict(qkv=e(mb, seq, 3 * h), ctx=e(mb, seq, h), attn=e(mb, seq, h), h1=e(mb, seq, h),
+                             inter=e(mb, seq, f), out=e(mb, seq, h), ping=e(mb, seq, h), pong=e(mb, seq, h))
             self._buf_key = key
         return self._buf
+
+    def _score_buffers(self, mb, seq):
+        """[mb, heads, S, S] scores and probabilities, only needed by the unfused attention path."""
+        buf = self._buf
+        if "scores" not in buf:
+            buf["scores"] = torch.empty(mb, self.heads, seq, seq, device=self.device, dtype=torch.float32)
+            buf["probs"] = torch.empty_like(buf["scores"])
+        return buf["scores"], buf["probs"]
 
     def _timed(self, kind, flops, nbytes, fn):
         self.launches += 1
         if self.timeline is None:
-            return fn()
+            r = fn()
+            if r is False:
+                self.launches -= 1
+            return r
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         r = fn()
         e.record()
+        if r is False:  # the op declined (fused attention not applicable): nothing was launched
+            self.launches -= 1
+            return r
         self.timeline.append((kind, flops, nbytes, s, e))
         return r
 
@@ -84,22 +101,20 @@ class BertEncoderB200:
         h, f, nh, d, mm = self.hidden, self.ffn, self.heads, self.head_dim, self.math_mode
         t = b * seq
         x2 = x.view(t, h)
-        qkv, scores, probs, ctx = buf["qkv"][:b], buf["scores"][:b], buf["probs"][:b], buf["ctx"][:b]
+        qkv, ctx = buf["qkv"][:b], buf["ctx"][:b]
         attn, h1, inter, out = buf["attn"][:b], buf["h1"][:b], buf["inter"][:b], buf["out"][:b]
 
         self._timed("gemm", 2 * t * 3 * h * h, 0, lambda: ops.matmul(
             x2, w["wqkv"], out=qkv.view(t, 3 * h), trans_b=True, epilogue=EPI_BIAS, bias=w["bqkv"], math_mode=mm))
-        # scores[b,n] = q[b,:,n,:] @ k[b,:,n,:]^T * 1/sqrt(d), heads addressed inside qkv
-        self._timed("gemm_qk", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
-            qkv, qkv[..., h:], scores, batch_outer=b, batch_inner=nh, M=seq, N=seq, K=d, lda=3 * h, ldb=3 * h,
-            ldy=seq, a_strides=(seq * 3 * h, d), b_strides=(seq * 3 * h, d), y_strides=(nh * seq * seq, seq * seq),
-            trans_b=True, epilogue=EPI_SCALE, scale=1.0 / math.sqrt(d), math_mode=mm))
-        self._timed("softmax", 0, 8 * b * nh * seq * seq, lambda: ops.softmax(scores, 3, out=probs))
-        # ctx[b,:,n,:] = probs[b,n] @ v[b,:,n,:]; written straight into [b, S, hidden]
-        self._timed("gemm_pv", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
-            probs, qkv[..., 2 * h:], ctx, batch_outer=b, batch_inner=nh, M=seq, N=d, K=seq, lda=seq, ldb=3 * h,
-            ldy=h, a_strides=(nh * seq * seq, seq * seq), b_strides=(seq * 3 * h, d), y_strides=(seq * h, d),
-            trans_b=False, math_mode=mm))
+        # MatMul -> Mul -> Softmax -> MatMul as one kernel when the fused attention covers the case
+        q4 = qkv.view(b, seq, 3 * nh, d)
+        fused = self.fused_attention and self._timed(
+            "attention", 4 * b * nh * seq * seq * d, 16 * t * h,
+            lambda: ops.attention_views(q4[:, :, :nh], q4[:, :, nh:2 * nh], q4[:, :, 2 * nh:], ctx.view(b, seq, nh, d),
+                                        1.0 / math.sqrt(d), math_mode=mm))
+        if fused is False:
+            scores, probs = self._score_buffers(buf["qkv"].shape[0], seq)
+            self._attention_unfused(qkv, scores[:b], probs[:b], ctx, b, seq)
         self._timed("gemm", 2 * t * h * h, 0, lambda: ops.matmul(
             ctx.view(t, h), w["wo"], out=attn.view(t, h), trans_b=True, epilogue=EPI_BIAS_RESIDUAL, bias=w["bo"],
             residual=x2, math_mode=mm))
@@ -112,6 +127,21 @@ class BertEncoderB200:
             residual=h1.view(t, h), math_mode=mm))
         self._timed("layernorm", 0, 8 * t * h, lambda: ops.layernorm(out, w["ln2_g"], w["ln2_b"], self.eps, out=y))
         return y
+
+    def _attention_unfused(self, qkv, scores, probs, ctx, b, seq):
+        h, nh, d, mm = self.hidden, self.heads, self.head_dim, self.math_mode
+        t = b * seq
+        # scores[b,n] = q[b,:,n,:] @ k[b,:,n,:]^T * 1/sqrt(d), heads addressed inside qkv
+        self._timed("gemm_qk", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
+            qkv, qkv[..., h:], scores, batch_outer=b, batch_inner=nh, M=seq, N=seq, K=d, lda=3 * h, ldb=3 * h,
+            ldy=seq, a_strides=(seq * 3 * h, d), b_strides=(seq * 3 * h, d), y_strides=(nh * seq * seq, seq * seq),
+            trans_b=True, epilogue=EPI_SCALE, scale=1.0 / math.sqrt(d), math_mode=mm))
+        self._timed("softmax", 0, 8 * b * nh * seq * seq, lambda: ops.softmax(scores, 3, out=probs))
+        # ctx[b,:,n,:] = probs[b,n] @ v[b,:,n,:]; written straight into [b, S, hidden]
+        self._timed("gemm_pv", 2 * b * nh * seq * seq * d, 4 * (2 * t * h + b * nh * seq * seq), lambda: ops.gemm_raw(
+            probs, qkv[..., 2 * h:], ctx, batch_outer=b, batch_inner=nh, M=seq, N=d, K=seq, lda=seq, ldb=3 * h,
+            ldy=h, a_strides=(nh * seq * seq, seq * seq), b_strides=(seq * 3 * h, d), y_strides=(seq * h, d),
+            trans_b=False, math_mode=mm))
 
     # -- whole encoder ------------------------------------------------------------------------------
     def forward_device(self, x, out=None):

@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 from ._lib import (ADD, DIV, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RELU, EPI_BIAS_RESIDUAL, EPI_NONE, EPI_SCALE, ERF,
-                   GELU, MATH_MODES, MUL, POW, RELU, SQRT, SUB, ConvDesc, GemmDesc, check)
+                   GELU, MATH_MODES, MUL, POW, RELU, SQRT, SUB, AttentionDesc, ConvDesc, GemmDesc, check)  # noqa: F401
 
 default_math_mode = "fp32x3"  # "fp32x3" | "tf32" | "fp32"; overridable per call
 
@@ -149,6 +149,27 @@ def gemm(A, B, C=None, out=None, *, alpha=1.0, beta=1.0, transA=0, transB=1, rel
     Y = matmul(A, B, out, trans_b=True, math_mode=math_mode)
     Y = add(Y, C, out=Y)
     return relu_(Y) if relu else Y
+
+
+def attention_views(q, k, v, out, scale, math_mode=None):
+    """Fused Softmax(q k^T * scale) v. q, k, v, out are 4-D [batch, seq, heads, head_dim] views (any
+    strides with head_dim contiguous, e.g. slices of a fused QKV projection). Returns False without
+    launching when the fused kernel does not cover the case (the caller then runs the nodes unfused)."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (out, "out")):
+        _chk(t, n)
+        if t.dim() != 4 or t.stride(3) != 1:
+            raise ValueError("%s must be a [batch, seq, heads, head_dim] view with contiguous head_dim" % n)
+    b, s, h, dh = q.shape
+    if tuple(k.shape) != (b, s, h, dh) or tuple(v.shape) != (b, s, h, dh) or tuple(out.shape) != (b, s, h, dh):
+        raise ValueError("attention: q, k, v, out must have the same shape")
+    d = AttentionDesc(b, h, s, dh, q.stride(1), q.stride(2), q.stride(0), k.stride(1), k.stride(2), k.stride(0),
+                      v.stride(1), v.stride(2), v.stride(0), out.stride(1), out.stride(2), out.stride(0),
+                      float(scale), _math(math_mode))
+    lib = _lib.load()
+    if not lib.b200_attention_supported(ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out)):
+        return False
+    check(lib.b200_attention_f32(_stream(), ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(out)))
+    return True
 
 
 def conv2d(X, W, B=None, out=None, *, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), group=1, relu=False,

@@ -100,6 +100,30 @@ typedef struct b200_gemm_desc {
 B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
                   const float *bias, const float *residual, float *Y);
 
+/* Fused attention: out = Softmax(Q K^T * scale, axis=-1) V per (batch, head), the node pattern
+ * MatMul -> Mul(constant) -> Softmax -> MatMul of the exported BERT graph (each node as in
+ * pure_implementations.py:130-235, :87-89, :346-366) without writing the [seq, seq] scores to memory.
+ * Q, K, V, out are [batch, seq, heads, head_dim] views given by element strides per row (token),
+ * head and batch, head_dim contiguous -- e.g. slices of a fused QKV projection, and out laid out as
+ * [batch, seq, hidden]. Implemented for math_mode TF32, head_dim 64, seq a multiple of 32 up to 384,
+ * scale > 0, 16-byte aligned Q/K/V with strides that are multiples of 4 and a 32-byte aligned out
+ * with strides that are multiples of 8; b200_attention_supported() says whether a call qualifies,
+ * anything else returns B200_EUNSUPPORTED and the caller runs the unfused nodes. */
+typedef struct b200_attention_desc {
+  int64_t batch, heads, seq, head_dim;
+  int64_t q_row, q_head, q_batch;
+  int64_t k_row, k_head, k_batch;
+  int64_t v_row, v_head, v_batch;
+  int64_t o_row, o_head, o_batch;
+  float scale;
+  int32_t math_mode;
+} b200_attention_desc;
+
+B200_API int b200_attention_supported(const b200_attention_desc *desc, const float *Q, const float *K,
+                                      const float *V, const float *out);
+B200_API int b200_attention_f32(void *stream, const b200_attention_desc *desc, const float *Q, const float *K,
+                                const float *V, float *out);
+
 /* ONNXConv (daceml/onnx/op_implementations/img_op_implementations.py:164-326): NCHW x OIHW
  * cross-correlation, group=1, dilation=1, symmetric zero padding (the padded form is what
  * daceml/transformation/pad_conv_fusion.py:77-95 folds into the node). bias may be NULL.
