@@ -344,6 +344,15 @@ def kernel_cases(device):
             return fn, 4 * b * h * s * s * d, 16 * b * s * h * d, "tensor"
         return make
 
+    def attn_fused_headmajor(b, h, s, d):
+        def make():
+            q, k, v = (rn(b, h, s, d) for _ in range(3))  # each head's [s, d] block contiguous
+            ctx = torch.empty(b, s, h * d, device=device)
+            fn = lambda: ops.attention_views(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),  # noqa
+                                             ctx.view(b, s, h, d), 0.125, math_mode="tf32")
+            return fn, 4 * b * h * s * s * d, 16 * b * s * h * d, "tensor"
+        return make
+
     def conv(n, c, hw, m, mode):
         def make():
             x = torch.rand(n, c, hw, hw, device=device, generator=g)
@@ -364,6 +373,7 @@ def kernel_cases(device):
         "gemm_fp32x3_ffn1": gemm(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU), "gemm_fp32x3_proj": gemm(16384, 768, 768, "fp32x3"),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
         "attention_fused_tf32": attn_fused(32, 16, 384, 64),
+        "attention_fused_tf32_headmajor": attn_fused_headmajor(32, 16, 384, 64),
     }
 
 

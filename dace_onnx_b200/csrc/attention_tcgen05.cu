@@ -2,15 +2,18 @@
 // the [S, S] score matrix in HBM. Replaces the node pattern MatMul -> Mul(const) -> Softmax ->
 // MatMul of the exported BERT graph (TF32 tensor-core mode).
 //
-// One persistent CTA per SM walks (batch, head) items. K and V of the item stay in shared memory
-// (K as the K-major B operand of Q K^T, V as the MN-major B operand of P V); the query tiles of
-// 128 rows stream through a single Q buffer. Per query tile:
-//   warp 1 issues Q K^T into TMEM columns [0, S)            (tcgen05.mma kind::tf32, A and B in smem)
-//   warps 2-5 (one score row per thread) read the row from TMEM, take its maximum, overwrite it in
-//             place with P = exp2((s - max) * scale * log2 e) and sum P          (tcgen05.ld / st)
+// One persistent CTA per SM walks (batch, head) items, 128 query rows at a time. Q is double
+// buffered; the head's K and V stream through a ring of 128-row blocks (K as the K-major B operand
+// of Q K^T, V as the MN-major B operand of P V), so loads run ahead of the MMAs across tiles and
+// heads. Per query tile:
+//   warp 0 loads Q, the key blocks and the value blocks                      (cp.async.bulk.tensor)
+//   warp 1 issues Q K^T block by block into TMEM columns [0, S)  (tcgen05.mma kind::tf32, A and B in smem)
+//   warps 2-9 (two per score row, alternating 32-column blocks) read the row from TMEM, take its
+//             maximum, overwrite it in place with P = exp2((s - max) * scale * log2 e) and sum P
+//             (tcgen05.ld / st)
 //   warp 1 issues P V with the A operand read from TMEM into columns [448, 512), 128 key columns
 //             at a time as soon as the softmax warps have published them
-//   warps 2-5 read the 64 output columns, divide by the row sum and store [row, head*64 .. +64).
+//   warps 2-9 read the 64 output columns, divide by the row sum and store [row, head*64 .. +64).
 // HBM traffic is Q, K, V once and the context once: 16 B per (token, head-dim element) instead of
 // the 4 * S * S * 4 B per head the unfused chain moves.
 //
@@ -24,15 +27,17 @@ namespace b200 {
 using namespace tc;
 namespace {
 
-constexpr int kD = 64;            // head dimension
-constexpr int kQBytes = 128 * kD * 4;   // 32 KiB: two k-blocks of [128 rows][128 B]
-constexpr int kOCol = 448;        // TMEM column of the output accumulator
+constexpr int kD = 64;                  // head dimension
+constexpr int kBlkBytes = 128 * kD * 4; // 32 KiB: 128 rows x 64 fp32 as two slices of [128 rows][128 B]
+constexpr int kRing = 5;                // K / V blocks in flight (shared memory: (2 + kRing) x 32 KiB)
+constexpr int kOCol = 448;              // TMEM column of the output accumulator
 constexpr int kMaxS = 384;
+constexpr int kThreads = 32 * (2 + 8);   // producer, MMA issuer, 8 softmax / output warps
 
 struct AttnParams {
-  int S, Sp;          // sequence length; Sp = S rounded up to 128 (row capacity of the K / V buffers)
+  int S;              // sequence length
   int heads;
-  int m_tiles;
+  int n_blocks;       // ceil(S / 128): query tiles per head, and key / value blocks per tile
   int64_t items;      // batch * heads
   float scale_log2e;
   float *out;
@@ -40,33 +45,37 @@ struct AttnParams {
   unsigned *status;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const uint32_t q_smem = smem_u32(smem);
-  const uint32_t kblk_bytes = (uint32_t)p.Sp * 128;  // one 32-wide slice of K or V: [Sp rows][128 B]
-  const uint32_t k_smem = q_smem + kQBytes;
-  const uint32_t v_smem = k_smem + 2 * kblk_bytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kQBytes + 4 * (size_t)kblk_bytes);
-  const uint32_t bar_kv_full = smem_u32(bars), bar_kv_empty = bar_kv_full + 8, bar_q_full = bar_kv_full + 16,
-                 bar_q_empty = bar_kv_full + 24, bar_s_full = bar_kv_full + 32, bar_o_full = bar_kv_full + 40,
-                 bar_o_empty = bar_kv_full + 48, bar_p_full = bar_kv_full + 56;  // p_full[0..3]
+  const uint32_t q_smem = smem_u32(smem);                   // two query-tile buffers
+  const uint32_t ring_smem = q_smem + 2 * kBlkBytes;        // kRing blocks of K or V
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (2 + kRing) * (size_t)kBlkBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t bar_q_full = bar0, bar_q_empty = bar0 + 16, bar_ring_full = bar0 + 32,
+                 bar_ring_empty = bar_ring_full + 8 * kRing, bar_s_full = bar_ring_empty + 8 * kRing,
+                 bar_o_full = bar_s_full + 8, bar_o_empty = bar_s_full + 16, bar_p_full = bar_s_full + 24;  // [4]
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_red[2][128];  // row maximum / row sum exchange between the two warps of a lane quarter
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    mbar_init(bar_kv_full, 1);
-    mbar_init(bar_kv_empty, 1);
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_q_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q_full + 8 * i, 1);
+      mbar_init(bar_q_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(bar_ring_full + 8 * i, 1);
+      mbar_init(bar_ring_empty + 8 * i, 1);
+    }
     mbar_init(bar_s_full, 1);
     mbar_init(bar_o_full, 1);
-    mbar_init(bar_o_empty, 128);
-    for (int c = 0; c < 4; ++c) mbar_init(bar_p_full + 8 * c, 128);
+    mbar_init(bar_o_empty, 256);
+    for (int c = 0; c < 4; ++c) mbar_init(bar_p_full + 8 * c, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -78,73 +87,102 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int *abort_flag = &s_abort;
-  const int n_chunks = (p.S + 127) / 128;  // 128-column groups of P handed to the P V MMAs
+  const int n_chunks = p.n_blocks;  // 128-column groups of P, one per value block
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
+    // Per query tile: Q (32 KiB), then the key blocks, then the value blocks of the head, each
+    // 128 rows x 64 as two [128][128 B] slices. K and V are re-read for every query tile of the
+    // head (they come from L2 the second and third time); in exchange every load runs ahead of
+    // the MMAs through the ring, across tiles and heads.
     if (lane == 0) {
-      uint32_t kv_ph = 0, q_ph = 0;
+      int rs = 0, qs = 0;
+      uint32_t r_ph = 0, q_ph = 0;
       bool ok = true;
       for (int64_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         const int b = (int)(item / p.heads), h = (int)(item % p.heads);
-        if (!(ok = mbar_wait(bar_kv_empty, kv_ph ^ 1, abort_flag, p.status, 1u))) break;
-        mbar_expect_tx(bar_kv_full, 4 * kblk_bytes);
-        for (int kb = 0; kb < 2; ++kb)
-          for (int r0 = 0; r0 < p.Sp; r0 += 128) {
-            tma_load_4d(k_smem + kb * kblk_bytes + r0 * 128, &map_k, bar_kv_full, kb * 32, r0, h, b);
-            tma_load_4d(v_smem + kb * kblk_bytes + r0 * 128, &map_v, bar_kv_full, kb * 32, r0, h, b);
+        for (int mt = 0; mt < p.n_blocks && ok; ++mt) {
+          if (!(ok = mbar_wait(bar_q_empty + 8 * qs, q_ph ^ 1, abort_flag, p.status, 1u))) break;
+          mbar_expect_tx(bar_q_full + 8 * qs, kBlkBytes);
+          tma_load_4d(q_smem + qs * kBlkBytes, &map_q, bar_q_full + 8 * qs, 0, mt * 128, h, b);
+          tma_load_4d(q_smem + qs * kBlkBytes + kBlkBytes / 2, &map_q, bar_q_full + 8 * qs, 32, mt * 128, h, b);
+          if (++qs == 2) { qs = 0; q_ph ^= 1; }
+          for (int j = 0; j < 2 * p.n_blocks; ++j) {
+            const bool is_v = j >= p.n_blocks;
+            const int r0 = (is_v ? j - p.n_blocks : j) * 128;
+            if (!(ok = mbar_wait(bar_ring_empty + 8 * rs, r_ph ^ 1, abort_flag, p.status, 1u))) break;
+            mbar_expect_tx(bar_ring_full + 8 * rs, kBlkBytes);
+            const uint32_t dst = ring_smem + rs * kBlkBytes;
+            const CUtensorMap *map = is_v ? &map_v : &map_k;
+            tma_load_4d(dst, map, bar_ring_full + 8 * rs, 0, r0, h, b);
+            tma_load_4d(dst + kBlkBytes / 2, map, bar_ring_full + 8 * rs, 32, r0, h, b);
+            if (++rs == kRing) { rs = 0; r_ph ^= 1; }
           }
-        kv_ph ^= 1;
-        for (int mt = 0; mt < p.m_tiles; ++mt) {
-          if (!(ok = mbar_wait(bar_q_empty, q_ph ^ 1, abort_flag, p.status, 1u))) break;
-          mbar_expect_tx(bar_q_full, kQBytes);
-          tma_load_4d(q_smem, &map_q, bar_q_full, 0, mt * 128, h, b);
-          tma_load_4d(q_smem + kQBytes / 2, &map_q, bar_q_full, 32, mt * 128, h, b);
-          q_ph ^= 1;
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     if (lane == 0) {
-      uint32_t kv_ph = 0, t_ph = 0;  // t_ph: phase of the per-tile barriers (q_full, o_empty, p_full, o_full)
+      int rs = 0, qs = 0;
+      uint32_t r_ph = 0, q_ph = 0, t_ph = 0;  // t_ph: phase of the per-tile barriers (o_empty, p_full, o_full)
+      // Descriptors are built once; inside the loops an MMA costs one 64-bit add on its operand
+      // descriptors (the start-address field counts 16-byte units), because this single thread's
+      // instruction latency, not the tensor core, would otherwise bound the small MMAs.
       const uint32_t idesc_o = make_idesc(kD, true);
+      const uint32_t idesc_full = make_idesc(128, false);
+      const uint64_t kdesc0 = make_smem_desc(0, 16, 1024, kLayoutSw128);                    // Q and K blocks
+      const uint64_t vdesc0 = make_smem_desc(0, kBlkBytes / 2, 512, kLayoutSw128Base32);   // V blocks
       bool ok = true;
       for (int64_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
-        if (!(ok = mbar_wait(bar_kv_full, kv_ph, abort_flag, p.status, 2u))) break;
-        kv_ph ^= 1;
-        for (int mt = 0; mt < p.m_tiles && ok; ++mt) {
-          if (!(ok = mbar_wait(bar_q_full, t_ph, abort_flag, p.status, 2u))) break;
-          tc_fence_after();
-          // S = Q K^T: N is issued in pieces of at most 256 columns
-          for (int n0 = 0; n0 < p.S; n0 += 256) {
-            const int n_len = p.S - n0 < 256 ? p.S - n0 : 256;
-            const uint32_t idesc_s = make_idesc(n_len, false);
+        for (int mt = 0; mt < p.n_blocks && ok; ++mt) {
+          if (!(ok = mbar_wait(bar_q_full + 8 * qs, q_ph, abort_flag, p.status, 2u))) break;
+          const uint64_t a_base = kdesc0 + ((q_smem + qs * kBlkBytes) >> 4);
+          // S[:, 128 j .. ] = Q K_j^T, one key block at a time as it lands
+          for (int j = 0; j < p.n_blocks && ok; ++j) {
+            if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 2u))) break;
+            tc_fence_after();
+            const int n_len = p.S - j * 128;
+            const uint32_t idesc_s = n_len >= 128 ? idesc_full : make_idesc(n_len, false);
+            const uint64_t b_base = kdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
+            const uint32_t d_tmem = tmem_base + j * 128;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-              const int kb = ks >> 2, kk = ks & 3;
-              const uint64_t a = make_smem_desc(q_smem + kb * (kQBytes / 2) + kk * 32, 16, 1024, kLayoutSw128);
-              const uint64_t bd = make_smem_desc(k_smem + kb * kblk_bytes + n0 * 128 + kk * 32, 16, 1024, kLayoutSw128);
-              umma_tf32(tmem_base + n0, a, bd, idesc_s, ks > 0 ? 1u : 0u);
+              // k-block kb = ks / 4 is half a block further (kBlkBytes / 2), k-step kk = ks % 4 is 32 B further
+              constexpr uint32_t kHalf = (kBlkBytes / 2) >> 4;
+              const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 2;
+              umma_tf32(d_tmem, a_base + off, b_base + off, idesc_s, ks > 0 ? 1u : 0u);
             }
+            umma_commit(bar_ring_empty + 8 * rs);
+            if (++rs == kRing) { rs = 0; r_ph ^= 1; }
           }
-          umma_commit(bar_q_empty);  // Q buffer reusable
-          umma_commit(bar_s_full);   // scores ready for the softmax warps
+          if (!ok) break;
+          umma_commit(bar_q_empty + 8 * qs);  // Q buffer reusable
+          umma_commit(bar_s_full);            // scores ready for the softmax warps
+          if (++qs == 2) { qs = 0; q_ph ^= 1; }
           // O = P V, A operand (P) from TMEM; the previous tile's O must have been read out
           if (!(ok = mbar_wait(bar_o_empty, t_ph ^ 1, abort_flag, p.status, 2u))) break;
           for (int c = 0; c < n_chunks && ok; ++c) {
             if (!(ok = mbar_wait(bar_p_full + 8 * c, t_ph, abort_flag, p.status, 4u))) break;
+            if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 4u))) break;
             tc_fence_after();
-            const int k_end = (c + 1) * 128 < p.S ? (c + 1) * 128 : p.S;
-            for (int k0 = c * 128; k0 < k_end; k0 += 8) {
-              // 8 key rows of V: [k0, k0+8) x 64, two 32-column chunks kblk_bytes apart
-              const uint64_t bd = make_smem_desc(v_smem + k0 * 128, kblk_bytes, 512, kLayoutSw128Base32);
-              umma_tf32_ts(tmem_base + kOCol, tmem_base + k0, bd, idesc_o, k0 > 0 ? 1u : 0u);
+            const uint64_t v_base = vdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
+            const uint32_t p_tmem = tmem_base + c * 128;
+            const int k_len = p.S - c * 128 < 128 ? p.S - c * 128 : 128;
+            // 8 key rows of V (8 x 128 B = 64 descriptor units) and 8 columns of P per MMA
+            if (k_len == 128) {
+#pragma unroll
+              for (int k8 = 0; k8 < 16; ++k8)
+                umma_tf32_ts(tmem_base + kOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (c > 0 || k8 > 0) ? 1u : 0u);
+            } else {
+              for (int k8 = 0; k8 * 8 < k_len; ++k8)
+                umma_tf32_ts(tmem_base + kOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (c > 0 || k8 > 0) ? 1u : 0u);
             }
+            umma_commit(bar_ring_empty + 8 * rs);
+            if (++rs == kRing) { rs = 0; r_ph ^= 1; }
           }
           if (!ok) break;
           umma_commit(bar_o_full);
-          if (mt + 1 == p.m_tiles) umma_commit(bar_kv_empty);  // K / V buffers reusable
           // P lives where the next tile's scores go: wait until the P V MMAs have consumed it
           if (!(ok = mbar_wait(bar_o_full, t_ph, abort_flag, p.status, 2u))) break;
           t_ph ^= 1;
@@ -152,64 +190,78 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
     }
   } else {
-    // ------------------------------- softmax + output (one row per thread) -------------------------------
+    // ------------------------------- softmax + output -------------------------------
+    // Two warps per TMEM lane quarter: `half` 0 takes the even 32-column blocks of the row, half 1
+    // the odd ones; row maximum and row sum are combined through shared memory, the pair meeting on
+    // a named barrier of its own. For the output each half normalises and stores 32 of the 64 columns.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int pair_bar = 1 + quarter;  // named barrier ids 1..4 (0 is __syncthreads)
     uint32_t t_ph = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
       const int b = (int)(item / p.heads), h = (int)(item % p.heads);
-      for (int mt = 0; mt < p.m_tiles; ++mt) {
+      for (int mt = 0; mt < p.n_blocks; ++mt) {
         if (!(ok = mbar_wait(bar_s_full, t_ph, abort_flag, p.status, 8u))) break;
         tc_fence_after();
         float mx = -INFINITY;
-        for (int c = 0; c < p.S; c += 32) {
+        for (int c = half * 32; c < p.S; c += 64) {
           uint32_t v[32];
           tmem_ld32(lane_addr + c, v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(v[j]));
         }
+        s_red[half][row_in_tile] = mx;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        mx = fmaxf(mx, s_red[half ^ 1][row_in_tile]);
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");  // both have read before s_red is reused
         const float off = mx * p.scale_log2e;
         float sum = 0.f;
-        for (int c = 0; c < p.S; c += 32) {
-          uint32_t v[32];
-          tmem_ld32(lane_addr + c, v);
-          tmem_ld_wait();
+        for (int ch = 0; ch < n_chunks; ++ch) {
+          const int c_end = (ch + 1) * 128 < p.S ? (ch + 1) * 128 : p.S;
+          for (int c = ch * 128 + half * 32; c < c_end; c += 64) {
+            uint32_t v[32];
+            tmem_ld32(lane_addr + c, v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float e = exp2f(fmaf(__uint_as_float(v[j]), p.scale_log2e, -off));
-            sum += e;
-            v[j] = __float_as_uint(e);
+            for (int j = 0; j < 32; ++j) {
+              float e;
+              asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(__uint_as_float(v[j]), p.scale_log2e, -off)));
+              sum += e;
+              v[j] = __float_as_uint(e);
+            }
+            tmem_st32(lane_addr + c, v);
           }
-          tmem_st32(lane_addr + c, v);
-          if (((c + 32) & 127) == 0 || c + 32 >= p.S) {
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bar_p_full + 8 * (c >> 7));
-          }
+          // every thread arrives once per 128-column group, whether or not it owned a block in it
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(bar_p_full + 8 * ch);
         }
+        s_red[half][row_in_tile] = sum;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        sum += s_red[half ^ 1][row_in_tile];
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         if (!(ok = mbar_wait(bar_o_full, t_ph, abort_flag, p.status, 8u))) break;
         tc_fence_after();
-        const int row = mt * 128 + quarter * 32 + lane;
+        const int row = mt * 128 + row_in_tile;
         const float inv = 1.0f / sum;
-        float *orow = p.out + (int64_t)b * p.o_batch + (int64_t)row * p.o_row + (int64_t)h * p.o_head;
-#pragma unroll
-        for (int c = 0; c < kD; c += 32) {
+        float *orow = p.out + (int64_t)b * p.o_batch + (int64_t)row * p.o_row + (int64_t)h * p.o_head + half * 32;
+        {
           uint32_t v[32];
-          tmem_ld32(lane_addr + kOCol + c, v);
+          tmem_ld32(lane_addr + kOCol + half * 32, v);
           tmem_ld_wait();
-          if (c + 32 >= kD) {
-            tc_fence_before();
-            mbar_arrive(bar_o_empty);  // the accumulator may be overwritten by the next tile
-          }
+          tc_fence_before();
+          mbar_arrive(bar_o_empty);  // the accumulator may be overwritten by the next tile
           if (row < p.S) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               float o[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) o[i] = __uint_as_float(v[j + i]) * inv;
-              asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow + c + j), "f"(o[0]), "f"(o[1]),
+              asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow + j), "f"(o[0]), "f"(o[1]),
                            "f"(o[2]), "f"(o[3]), "f"(o[4]), "f"(o[5]), "f"(o[6]), "f"(o[7])
                            : "memory");
             }
@@ -270,9 +322,8 @@ int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, 
   if (int rc = encode_qkv_map(&mv, V, d, d.v_row, d.v_head, d.v_batch, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
   AttnParams p{};
   p.S = (int)d.seq;
-  p.Sp = (int)((d.seq + 127) / 128 * 128);
   p.heads = (int)d.heads;
-  p.m_tiles = p.Sp / 128;
+  p.n_blocks = (int)((d.seq + 127) / 128);
   p.items = d.batch * d.heads;
   p.scale_log2e = d.scale * 1.4426950408889634f;
   p.out = out;
@@ -281,11 +332,11 @@ int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, 
   p.o_head = d.o_head;
   p.status = device_status_ptr();
   if (!p.status) return fail(B200_ECUDA, "attention: device status word unavailable");
-  const int smem = kQBytes + 4 * p.Sp * 128 + 1024 + 128;
+  const int smem = (2 + kRing) * kBlkBytes + 1024 + 256;
   if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return fail(B200_ECUDA, "attention: cannot set dynamic shared memory to %d", smem);
   const int64_t grid = p.items < kNumSMs ? p.items : kNumSMs;
-  attention_tc_kernel<<<(unsigned)grid, 192, smem, st>>>(mq, mk, mv, p);
+  attention_tc_kernel<<<(unsigned)grid, kThreads, smem, st>>>(mq, mk, mv, p);
   return check_launch("attention_tc");
 }
 

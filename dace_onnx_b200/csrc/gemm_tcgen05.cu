@@ -6,11 +6,11 @@
 //               (128B-swizzled, 32 fp32 of K per block) into a ring of shared-memory stages;
 //   warp 1      MMA issuer: allocates TMEM, one lane issues tcgen05.mma for each 8-wide k-step
 //               and commits stage release / accumulator-ready events to mbarriers;
-//   warps 2-9   epilogue: tcgen05.ld the fp32 accumulator (row = TMEM lane, one row per thread, two
-//               warps per lane quarter), apply the fused epilogue (bias / ReLU / erf-Gelu /
+//   next 8 or 16 warps: epilogue: tcgen05.ld the fp32 accumulator (row = TMEM lane, one row per thread,
+//               two or four warps per lane quarter), apply the fused epilogue (bias / ReLU / erf-Gelu /
 //               residual / scale) and store with 256-bit vector stores, each thread writing whole
 //               32-byte sectors of its row (128-bit / scalar stores when Y is less aligned);
-//   warps 10-13 (3xTF32 mode only) split warps: rewrite each landed stage in place as
+//   last 4 warps (3xTF32 mode only) split warps: rewrite each landed stage in place as
 //               hi = tf32(x) and write lo = tf32(x - hi) beside it, so that the issuer can run
 //               lo*hi + hi*lo + hi*hi into the same fp32 accumulator (fp32-accurate products).
 // Two TMEM accumulators alternate so that the epilogue of tile i overlaps the MMAs of tile i+1.
@@ -61,7 +61,6 @@ struct GemmParams {
 
 // k-blocks per in-core accumulation chunk in 3xTF32 mode (2 x 32 = 64 values of K, 24 MMAs).
 constexpr int kSplitChunkKb = 2;
-constexpr int kEpilogueWarps = 8;
 
 __device__ __forceinline__ void ld_global_v8(const float *p, float *v) {
   asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -175,10 +174,15 @@ struct Cfg {
   static constexpr int kStageBytes = (A_STAGE_BYTES + kBStageBytes) * (SPLIT3 ? 2 : 1);
   static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; BN is a power of two
+  // Epilogue warps: four per 64 accumulator columns, i.e. 2 (BN=64), 2 (BN=128, 3xTF32 keeps its
+  // column sums in registers), 4 warps per TMEM lane quarter for the wide TF32 tiles, whose erf-Gelu
+  // epilogue would otherwise take as long as the tile's MMAs.
+  static constexpr int kWarpsPerQuarter = (BN >= 128 && !SPLIT3) ? 4 : 2;
+  static constexpr int kEpilogueWarps = 4 * kWarpsPerQuarter;
   static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps + (SPLIT3 ? 4 : 0));
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int kColsPerWarp = BN / 2;  // two epilogue warps share each TMEM lane quarter
+  static constexpr int kColsPerWarp = BN / kWarpsPerQuarter;
 };
 
 template <int BN, bool B_MN, bool SPLIT3, bool CONV>
@@ -212,7 +216,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, kEpilogueWarps * 32);
+      mbar_init(bar_tempty + 8 * a, C::kEpilogueWarps * 32);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -228,8 +232,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   auto stage_a = [&](int s) { return smem_base + s * C::kStageBytes; };
   auto stage_b = [&](int s) { return smem_base + s * C::kStageBytes + A_STAGE_BYTES; };
-  auto stage_a_lo = [&](int s) { return smem_base + s * C::kStageBytes + A_STAGE_BYTES + C::kBStageBytes; };
-  auto stage_b_lo = [&](int s) { return smem_base + s * C::kStageBytes + 2 * A_STAGE_BYTES + C::kBStageBytes; };
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -297,7 +299,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // error that grows with the number of additions times |accumulator|, so the long sum is
     // formed by the epilogue warps in registers (round-to-nearest) from short in-core sums.
     if (lane == 0) {
+      // Descriptors are built once (address 0) and advanced with 64-bit adds: the start-address
+      // field counts 16-byte units, so a stage offset or a k-step is one addition. Keeping the
+      // per-MMA instruction count minimal matters: a single thread issues the MMAs, and with
+      // descriptor construction inside the loop its instruction latency (~140 clk per MMA), not the
+      // tensor core (128 clk per N=256 MMA), bounded the loop.
       constexpr uint32_t idesc = make_idesc(BN, B_MN);
+      constexpr uint32_t kStage16 = C::kStageBytes >> 4;
+      constexpr uint32_t kAStep = (UMMA_K * 4) >> 4;                         // 32 B inside the swizzle row
+      constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);  // next 8 k-rows, or 32 B
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + A_STAGE_BYTES, BK * 128, 512, kLayoutSw128Base32)
+                                    : make_smem_desc(smem_base + A_STAGE_BYTES, 16, 1024, kLayoutSw128);
+      constexpr uint32_t kALo16 = (A_STAGE_BYTES + C::kBStageBytes) >> 4;  // hi -> lo copy of the same operand
       const int chunk = SPLIT3 ? kSplitChunkKb : p.num_kb;
       int s = 0;
       uint32_t ph = 0;
@@ -313,24 +327,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int kb = kb0; kb < kb_end; ++kb) {
             if (!(ok = mbar_wait((SPLIT3 ? bar_split : bar_full) + 8 * s, ph, abort_flag, p.status, 4u))) break;
             tc_fence_after();
+            const uint64_t a_hi = a_desc0 + (uint32_t)s * kStage16;
+            const uint64_t b_hi = b_desc0 + (uint32_t)s * kStage16;
+            const uint32_t first = kb > kb0 ? 1u : 0u;  // 0: the chunk's first MMA overwrites the accumulator
 #pragma unroll
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-              const uint32_t a_off = kk * UMMA_K * 4;                     // 32 B inside the swizzle row
-              const uint32_t b_off = B_MN ? kk * 1024 : kk * UMMA_K * 4;  // next 8 k-rows, or 32 B
-              const uint32_t b_lbo = B_MN ? BK * 128 : 16;
-              const uint32_t b_sbo = B_MN ? 512 : 1024;
-              const uint32_t b_layout = B_MN ? kLayoutSw128Base32 : kLayoutSw128;
-              const uint64_t a_hi = make_smem_desc(stage_a(s) + a_off, 16, 1024, kLayoutSw128);
-              const uint64_t b_hi = make_smem_desc(stage_b(s) + b_off, b_lbo, b_sbo, b_layout);
-              const uint32_t accumulate = (kb > kb0 || kk > 0) ? 1u : 0u;  // 0 overwrites the accumulator
+              const uint32_t accumulate = kk > 0 ? 1u : first;
               if (SPLIT3) {
-                const uint64_t a_lo = make_smem_desc(stage_a_lo(s) + a_off, 16, 1024, kLayoutSw128);
-                const uint64_t b_lo = make_smem_desc(stage_b_lo(s) + b_off, b_lbo, b_sbo, b_layout);
-                umma_tf32(d_tmem, a_lo, b_hi, idesc, accumulate);  // small terms first
-                umma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
-                umma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+                umma_tf32(d_tmem, a_hi + kALo16 + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);  // lo * hi
+                umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kALo16 + kk * kBStep, idesc, 1u);          // hi * lo
+                umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, 1u);                   // hi * hi
               } else {
-                umma_tf32(d_tmem, a_hi, b_hi, idesc, accumulate);
+                umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);
               }
             }
             umma_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
@@ -342,9 +350,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
       }
     }
-  } else if (warp < 2 + kEpilogueWarps) {
+  } else if (warp < 2 + C::kEpilogueWarps) {
     // ------------------------------- epilogue -------------------------------
-    // Warp w reads TMEM lanes [32*(w%4), +32); the two warps of a lane quarter split the columns.
+    // Warp w reads TMEM lanes [32*(w%4), +32); the warps of a lane quarter split the columns.
     const int ew = warp - 2;
     const int quarter = warp & 3;
     const int col0 = (ew >> 2) * C::kColsPerWarp;
