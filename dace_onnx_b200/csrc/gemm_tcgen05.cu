@@ -18,6 +18,7 @@
 // Every mbarrier wait is bounded by a cycle budget; on expiry the CTA sets a bit in the device
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "contract.cuh"
@@ -47,6 +48,7 @@ struct GemmParams {
   int num_kb;
   int num_m_tiles, num_n_tiles;
   int64_t num_tiles;
+  int64_t num_tiles_batch;  // number of batch matrices (pair kernel: tiles = m pairs x n tiles x this)
   int batch_inner;
   int a_bi, a_bo, b_bi, b_bo;  // 1 when the operand advances with that batch index, 0 when broadcast
   int vec;                     // widest aligned access to Y / residual rows: 8, 4 or 1 floats
@@ -478,6 +480,201 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA-pair variant (TF32 mode, dense GEMM): a cluster of two CTAs computes a 256 x BN tile.
+// Each CTA loads its 128 rows of A and HALF of the B tile (BN/2 columns); the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads B from both CTAs' shared memory and writes each
+// CTA's 128 x BN accumulator into its own TMEM. Per FLOP this halves the B traffic from L2 into
+// shared memory, the B operand reads of the tensor core and the number of MMA instructions, and
+// leaves room for six pipeline stages. Roles per CTA are as in the single-CTA kernel; barriers:
+//   full[s]    in the even CTA, 2 arrivals (one expect_tx per CTA) + the bytes of both CTAs' loads
+//   empty[s]   in each CTA, 1 arrival: the even CTA commits to both
+//   tfull[a]   in each CTA, 1 arrival: the even CTA commits to both
+//   tempty[a]  in the even CTA, one arrival per epilogue thread of both CTAs
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+struct Cfg2 {
+  static constexpr int kBHalfBytes = (BN / 2) * BK * 4;
+  static constexpr int kStageBytes = A_STAGE_BYTES + kBHalfBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kWarpsPerQuarter = 4;
+  static constexpr int kEpilogueWarps = 4 * kWarpsPerQuarter;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kColsPerWarp = BN / kWarpsPerQuarter;
+};
+
+template <int BN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2<BN>::kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+  using C = Cfg2<BN>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t rank = cluster_ctarank();  // 0: issues the MMAs, 1: its partner
+  const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps * 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&s_tmem_base), C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before either touches the other's
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int *abort_flag = &s_abort;
+  // p.num_m_tiles counts 256-row tile pairs here
+  const int64_t num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * (p.num_tiles_batch);
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int n_t = (int)(tile % p.num_n_tiles);
+        const int64_t r = tile / p.num_n_tiles;
+        const int m_t = (int)(r % p.num_m_tiles);
+        const int64_t batch = r / p.num_m_tiles;
+        const int bo = (int)(batch / p.batch_inner), bi = (int)(batch % p.batch_inner);
+        const int row0 = (2 * m_t + (int)rank) * BM;
+        const int col0 = n_t * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
+          const uint32_t full_pair = map_to_cta(bar_full + 8 * s, 0);  // the even CTA's barrier
+          mbar_expect_tx_cluster(full_pair, A_STAGE_BYTES + C::kBHalfBytes);
+          const uint32_t a_dst = smem_base + s * C::kStageBytes, b_dst = a_dst + A_STAGE_BYTES;
+          tma_load_4d_pair(a_dst, &map_a, full_pair, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_4d_pair(b_dst + j * (BK * 128), &map_b, full_pair, col0 + 32 * j, kb * BK, bi * p.b_bi,
+                               bo * p.b_bo);
+          } else {
+            tma_load_4d_pair(b_dst, &map_b, full_pair, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (even CTA only) -------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_pair(BN, B_MN);
+      constexpr uint32_t kStage16 = C::kStageBytes >> 4;
+      constexpr uint32_t kAStep = (UMMA_K * 4) >> 4;
+      constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + A_STAGE_BYTES, BK * 128, 512, kLayoutSw128Base32)
+                                    : make_smem_desc(smem_base + A_STAGE_BYTES, 16, 1024, kLayoutSw128);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 2u))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 4u))) break;
+          tc_fence_after();
+          const uint64_t a_d = a_desc0 + (uint32_t)s * kStage16, b_d = b_desc0 + (uint32_t)s * kStage16;
+          const uint32_t first = kb > 0 ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk)
+            umma_tf32_pair(d_tmem, a_d + kk * kAStep, b_d + kk * kBStep, idesc, kk > 0 ? 1u : first);
+          // the stage is reusable in both CTAs once these MMAs have read it
+          umma_commit_pair(bar_empty + 8 * s);
+          umma_commit_pair(map_to_cta(bar_empty + 8 * s, 1));
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(bar_tfull + 8 * acc);
+        umma_commit_pair(map_to_cta(bar_tfull + 8 * acc, 1));
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs, own 128 rows) -------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int col0 = (ew >> 2) * C::kColsPerWarp;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int n_t = (int)(tile % p.num_n_tiles);
+      const int64_t r = tile / p.num_n_tiles;
+      const int m_t = (int)(r % p.num_m_tiles);
+      const int64_t batch = r / p.num_m_tiles;
+      const int64_t bo = batch / p.batch_inner, bi = batch % p.batch_inner;
+      const int64_t m = (int64_t)(2 * m_t + (int)rank) * BM + quarter * 32 + lane;
+      const int64_t row_off = bo * p.y_stride_outer + bi * p.y_stride_inner + m * p.ldy;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
+      tc_fence_after();
+      const uint32_t tempty_pair = map_to_cta(bar_tempty + 8 * acc, 0);
+#pragma unroll 1
+      for (int c = 0; c < C::kColsPerWarp; c += 32) {
+        uint32_t v[32];
+        float f[32];
+        tmem_ld32(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
+        tmem_ld_wait();
+        if (c + 32 >= C::kColsPerWarp) {
+          tc_fence_before();
+          mbar_arrive_cluster(tempty_pair);  // this thread is done with the accumulator
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        finish_row32(p, f, m, row_off, (int64_t)n_t * BN + col0 + c);
+      }
+      if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+
+  // Teardown: neither CTA may leave while its partner can still signal its barriers or read its
+  // shared memory through the pair's MMAs.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (s_abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side: tensor-map encoding and launch
 // ---------------------------------------------------------------------------------------------
 // A batch axis that is broadcast (stride 0) or trivial (extent 1) is encoded with extent 1 and a
@@ -504,6 +701,18 @@ int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, Ge
   const int64_t grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
   kern<<<(unsigned)grid, C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_tc");
+}
+
+template <int BN, bool B_MN>
+int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
+  using C = Cfg2<BN>;
+  auto kern = gemm_tc_pair_kernel<BN, B_MN>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+    return fail(B200_ECUDA, "gemm(tc pair): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * p.num_tiles_batch;
+  int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
+  kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
+  return check_launch("gemm_tc_pair");
 }
 
 template <bool B_MN, bool SPLIT3>
@@ -543,6 +752,16 @@ int launch_conv_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtenso
 }
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// EXPERIMENT switch while the pair kernel is being validated: B200_GEMM_PAIR=0 disables it.
+bool use_pair_kernel() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("B200_GEMM_PAIR");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
 
 int pick_bn(int64_t N, bool split3) {
   const int cands[3] = {256, 128, 64};
@@ -617,6 +836,8 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
             const float *residual, float *Y) {
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   const int bn = pick_bn(d.N, split3);
+  // CTA pairs (256 x 256 tiles) for TF32 GEMMs with wide N and at least two row tiles per matrix
+  const bool pair = !split3 && bn == 256 && d.M > BM && use_pair_kernel();
 
   CUtensorMap ma, mb;
   GemmParams p{};
@@ -641,7 +862,7 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
     str[0] = (uint64_t)d.ldb * 4;
     batch_axis(d.batch_inner, d.b_stride_inner, fb, &dims[2], &str[1], &p.b_bi);
     batch_axis(d.batch_outer, d.b_stride_outer, fb, &dims[3], &str[2], &p.b_bo);
-    if (int rc = encode_map(&mb, B, dims, str, d.trans_b ? BK : 32, d.trans_b ? (uint32_t)bn : BK,
+    if (int rc = encode_map(&mb, B, dims, str, d.trans_b ? BK : 32, d.trans_b ? (uint32_t)(pair ? bn / 2 : bn) : BK,
                             d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
       return rc;
   }
@@ -670,6 +891,11 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   p.status = device_status_ptr();
   if (!p.status) return fail(B200_ECUDA, "gemm(tc): device status word unavailable");
 
+  if (pair) {
+    p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));  // 256-row tile pairs
+    p.num_tiles_batch = d.batch_outer * d.batch_inner;
+    return d.trans_b ? launch_pair<256, false>(st, ma, mb, p) : launch_pair<256, true>(st, ma, mb, p);
+  }
   if (d.trans_b) {
     return split3 ? launch_bn<false, true>(st, bn, ma, mb, p) : launch_bn<false, false>(st, bn, ma, mb, p);
   }

@@ -57,6 +57,7 @@ class BertEncoderB200:
                 ln2_g=dev(p["ln2_g"]), ln2_b=dev(p["ln2_b"])))
         self._buf_key = None
         self._buf = None
+        self._io = None            # staging buffers and copy streams of forward_host
         self.launches = 0          # C-ABI kernel launches issued so far
         self.timeline = None       # when a list: (kind, flops, bytes, start_event, end_event) per launch
 
@@ -164,13 +165,62 @@ class BertEncoderB200:
         return out
 
     def __call__(self, x_host, out_host=None):
-        """Host entry: copies a (preferably pinned) host tensor in, runs, copies the result back."""
-        x = x_host.to(self.device, non_blocking=True)
-        y = self.forward_device(x)
+        """Host entry: host tensor in, host tensor out (see forward_host)."""
         if out_host is None:
-            return y.cpu()
-        out_host.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            out_host = torch.empty(tuple(x_host.shape), dtype=torch.float32, pin_memory=True)
+        self.forward_host(x_host, out_host)
+        torch.cuda.current_stream(self.device).synchronize()
+        return out_host
+
+    def forward_host(self, x_host, out_host, out_device=None):
+        """Host buffers in and out, copies overlapped with compute.
+
+        The batch moves in micro-batches through three streams: host->device copies on a copy-in
+        stream into two alternating staging buffers, the layers on the current stream, and
+        device->host copies of finished micro-batches on a copy-out stream, ordered by events. With
+        pinned host tensors the copies of micro-batch i+1 and i-1 run while micro-batch i computes.
+        `out_device` ([B, S, hidden] on the device, optional) also keeps the result resident, e.g.
+        for the output all-gather. Returns after enqueueing; the caller synchronises the current
+        stream (the last device->host copy is joined into it).
+        """
+        if x_host.dim() != 3 or x_host.shape[2] != self.hidden or x_host.dtype != torch.float32:
+            raise ValueError("expected a float32 [B, S, %d] host tensor" % self.hidden)
+        if tuple(out_host.shape) != tuple(x_host.shape):
+            raise ValueError("out_host must have the input's shape")
+        bsz, seq, _ = x_host.shape
+        mb = min(self.micro_batch, max(bsz, 1))
+        buf = self._buffers(mb, seq)
+        if self._io is None or self._io[0] != (mb, seq):
+            e = lambda: torch.empty(mb, seq, self.hidden, device=self.device, dtype=torch.float32)  # noqa: E731
+            self._io = ((mb, seq), [e(), e()], [e(), e()], torch.cuda.Stream(self.device), torch.cuda.Stream(self.device))
+        _, x_stage, y_stage, s_in, s_out = self._io
+        main = torch.cuda.current_stream(self.device)
+        s_in.wait_stream(main)   # staging buffers may still be in use by earlier work on the main stream
+        s_out.wait_stream(main)
+        ev_in, ev_done, ev_out = [], [], []
+        for i, b0 in enumerate(range(0, bsz, mb)):
+            b = min(mb, bsz - b0)
+            slot = i % 2
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_done[i - 2])  # the layers have consumed this staging buffer
+                x_stage[slot][:b].copy_(x_host[b0:b0 + b], non_blocking=True)
+                ev_in.append(s_in.record_event())
+            main.wait_event(ev_in[i])
+            if i >= 2:
+                main.wait_event(ev_out[i - 2])  # the previous result in this slot has left for the host
+            dst = out_device[b0:b0 + b] if out_device is not None else y_stage[slot][:b]
+            cur = x_stage[slot][:b]
+            for li, w in enumerate(self.layers):
+                last = li + 1 == len(self.layers)
+                nxt = dst if last else (buf["ping"][:b] if li % 2 == 0 else buf["pong"][:b])
+                cur = self._layer(cur, nxt, w, buf, b, seq)
+            ev_done.append(main.record_event())
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[i])
+                out_host[b0:b0 + b].copy_(dst, non_blocking=True)
+                ev_out.append(s_out.record_event())
+        main.wait_stream(s_out)
         return out_host
 
     # -- work model (algorithmic figures used by the roofline report) ---------------------------------

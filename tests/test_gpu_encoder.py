@@ -50,6 +50,20 @@ def test_micro_batching_and_stacking_do_not_change_results(cuda):
     assert torch.equal(whole, pieces)  # ragged last micro-batch, bit-identical rows
 
 
+def test_host_entry_overlapped_copies_match_device_path(cuda):
+    layers = [po.make_bert_layer_params(128, 256, seed=40 + i, std=0.05) for i in range(2)]
+    enc = BertEncoderB200(layers, heads=2, device=cuda, micro_batch=2)
+    x = torch.randn(7, 64, 128, generator=torch.Generator().manual_seed(41)).pin_memory()
+    y_host = torch.empty(7, 64, 128).pin_memory()
+    y_dev = torch.empty(7, 64, 128, device=cuda)
+    for _ in range(2):  # second pass reuses the staging buffers and streams
+        enc.forward_host(x, y_host, out_device=y_dev)
+        torch.cuda.synchronize()
+        ref = enc.forward_device(x.to(cuda))
+        assert torch.equal(y_dev, ref) and torch.equal(y_host, ref.cpu())
+    assert torch.equal(enc(x), ref.cpu())  # __call__ without a device copy of the output
+
+
 def test_rejects_wrong_inputs(cuda):
     enc = BertEncoderB200([po.make_bert_layer_params(128, 256, seed=1)], heads=2, device=cuda)
     with pytest.raises(ValueError):
