@@ -18,7 +18,6 @@
 // Every mbarrier wait is bounded by a cycle budget; on expiry the CTA sets a bit in the device
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "contract.cuh"
@@ -486,11 +485,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // CTA's 128 x BN accumulator into its own TMEM. Per FLOP this halves the B traffic from L2 into
 // shared memory, the B operand reads of the tensor core and the number of MMA instructions, and
 // leaves room for six pipeline stages. Roles per CTA are as in the single-CTA kernel; barriers:
-//   full[s]    in the even CTA, 2 arrivals (one expect_tx per CTA) + the bytes of both CTAs' loads
+//   full[s]    in the even CTA, 1 arrival (its expect_tx for both CTAs' bytes) + those bytes
 //   empty[s]   in each CTA, 1 arrival: the even CTA commits to both
 //   tfull[a]   in each CTA, 1 arrival: the even CTA commits to both
 //   tempty[a]  in the even CTA, one arrival per epilogue thread of both CTAs
 // ---------------------------------------------------------------------------------------------
+
 template <int BN>
 struct Cfg2 {
   static constexpr int kBHalfBytes = (BN / 2) * BK * 4;
@@ -528,12 +528,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 2);
+      mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps * 32);
+      mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps);  // one arrival per epilogue warp of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -556,6 +556,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      const uint32_t full_pair0 = map_to_cta(bar_full, 0);
       for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int n_t = (int)(tile % p.num_n_tiles);
         const int64_t r = tile / p.num_n_tiles;
@@ -566,17 +567,33 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int col0 = n_t * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
-          const uint32_t full_pair = map_to_cta(bar_full + 8 * s, 0);  // the even CTA's barrier
-          mbar_expect_tx_cluster(full_pair, A_STAGE_BYTES + C::kBHalfBytes);
+          // One expect_tx per stage, posted locally by the even CTA for the bytes of BOTH CTAs; the
+          // partner only issues its loads, whose completions are counted on the even CTA's barrier.
+          // (Its bytes can only arrive after the stage's previous phase has completed, because its
+          // own `empty` wait above is released by a commit that follows that completion.)
           const uint32_t a_dst = smem_base + s * C::kStageBytes, b_dst = a_dst + A_STAGE_BYTES;
-          tma_load_4d_pair(a_dst, &map_a, full_pair, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
-          if (B_MN) {
+          if (rank == 0) {
+            const uint32_t full = bar_full + 8 * s;
+            mbar_expect_tx(full, 2 * (A_STAGE_BYTES + C::kBHalfBytes));
+            tma_load_4d(a_dst, &map_a, full, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_4d_pair(b_dst + j * (BK * 128), &map_b, full_pair, col0 + 32 * j, kb * BK, bi * p.b_bi,
-                               bo * p.b_bo);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_4d(b_dst + j * (BK * 128), &map_b, full, col0 + 32 * j, kb * BK, bi * p.b_bi, bo * p.b_bo);
+            } else {
+              tma_load_4d(b_dst, &map_b, full, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
+            }
           } else {
-            tma_load_4d_pair(b_dst, &map_b, full_pair, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
+            const uint32_t full_pair = full_pair0 + 8 * s;  // the even CTA's barrier (shared::cluster address)
+            tma_load_4d_pair(a_dst, &map_a, full_pair, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_4d_pair(b_dst + j * (BK * 128), &map_b, full_pair, col0 + 32 * j, kb * BK, bi * p.b_bi,
+                                 bo * p.b_bo);
+            } else {
+              tma_load_4d_pair(b_dst, &map_b, full_pair, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
+            }
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -610,13 +627,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int kk = 0; kk < BK / UMMA_K; ++kk)
             umma_tf32_pair(d_tmem, a_d + kk * kAStep, b_d + kk * kBStep, idesc, kk > 0 ? 1u : first);
           // the stage is reusable in both CTAs once these MMAs have read it
-          umma_commit_pair(bar_empty + 8 * s);
-          umma_commit_pair(map_to_cta(bar_empty + 8 * s, 1));
+          umma_commit_pair_both(bar_empty + 8 * s, 3);
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
-        umma_commit_pair(bar_tfull + 8 * acc);
-        umma_commit_pair(map_to_cta(bar_tfull + 8 * acc, 1));
+        umma_commit_pair_both(bar_tfull + 8 * acc, 3);
         if (++acc == 2) { acc = 0; acc_ph ^= 1; }
       }
     }
@@ -647,8 +662,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tmem_ld32(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
         tmem_ld_wait();
         if (c + 32 >= C::kColsPerWarp) {
+          // this warp is done with the accumulator: one (possibly remote) arrival per warp
           tc_fence_before();
-          mbar_arrive_cluster(tempty_pair);  // this thread is done with the accumulator
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty_pair);
         }
 #pragma unroll
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
@@ -709,8 +726,30 @@ int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, G
   auto kern = gemm_tc_pair_kernel<BN, B_MN>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
     return fail(B200_ECUDA, "gemm(tc pair): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  // A persistent grid must not exceed the clusters the device can hold at once (both CTAs of a
+  // pair sit in one GPC, so this is fewer than SMs / 2); extra clusters would run a second wave alone.
+  static int max_pairs[64] = {};  // per device; the answer depends only on the kernel and its resources
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ECUDA, "gemm(tc pair): bad device");
+  if (max_pairs[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kNumSMs, 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1)
+      return fail(B200_ECUDA, "gemm(tc pair): cudaOccupancyMaxActiveClusters failed");
+    max_pairs[dev] = n;
+  }
   const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * p.num_tiles_batch;
-  int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
+  const int64_t pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
   kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_tc_pair");
 }
@@ -752,16 +791,6 @@ int launch_conv_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtenso
 }
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-
-// EXPERIMENT switch while the pair kernel is being validated: B200_GEMM_PAIR=0 disables it.
-bool use_pair_kernel() {
-  static int v = -1;
-  if (v < 0) {
-    const char *e = getenv("B200_GEMM_PAIR");
-    v = (e && e[0] == '0') ? 0 : 1;
-  }
-  return v == 1;
-}
 
 int pick_bn(int64_t N, bool split3) {
   const int cands[3] = {256, 128, 64};
@@ -837,7 +866,7 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   const int bn = pick_bn(d.N, split3);
   // CTA pairs (256 x 256 tiles) for TF32 GEMMs with wide N and at least two row tiles per matrix
-  const bool pair = !split3 && bn == 256 && d.M > BM && use_pair_kernel();
+  const bool pair = !split3 && bn == 256 && d.M > BM;
 
   CUtensorMap ma, mb;
   GemmParams p{};
@@ -989,3 +1018,4 @@ int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const fl
 }
 
 }  // namespace b200
+

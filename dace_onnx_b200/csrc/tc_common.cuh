@@ -227,6 +227,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
 }
+// the same arrival delivered to the barrier at this shared-memory offset in every CTA of `cta_mask`
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(cta_mask)
+      : "memory");
+}
 __host__ __device__ constexpr uint32_t make_idesc_pair(int n, bool b_mn_major) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
