@@ -54,8 +54,10 @@ __device__ __forceinline__ void st_stream4(float *p, float4 v) {
 
 // erf-based Gelu exactly as the exported node chain computes it:
 // Div(x, sqrt2) -> Erf -> Add 1 -> Mul x -> Mul 0.5.
+// The division by sqrt(2) is a multiplication by 1/sqrt(2) (<= 1 ulp apart): an IEEE division per
+// element would dominate the GEMM epilogue that calls this 128 times per thread and tile.
 __device__ __forceinline__ float gelu_erf(float x) {
-  float t = erff(x / 1.41421356237309504880f);
+  float t = erff(x * 0.70710678118654752440f);
   return (x * (t + 1.0f)) * 0.5f;
 }
 

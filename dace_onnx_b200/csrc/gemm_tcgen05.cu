@@ -494,7 +494,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int BN>
 struct Cfg2 {
   static constexpr int kBHalfBytes = (BN / 2) * BK * 4;
-  static constexpr int kStageBytes = A_STAGE_BYTES + kBHalfBytes;
+  // Two k-blocks per pipeline stage: the issuing thread pays its barrier wait, commit and loop
+  // overhead once per eight MMAs instead of once per four, which keeps it ahead of the tensor core.
+  static constexpr int kKbPerStage = 2;
+  static constexpr int kStageBytes = kKbPerStage * (A_STAGE_BYTES + kBHalfBytes);
   static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;
   static constexpr int kWarpsPerQuarter = 4;
@@ -565,34 +568,39 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int bo = (int)(batch / p.batch_inner), bi = (int)(batch % p.batch_inner);
         const int row0 = (2 * m_t + (int)rank) * BM;
         const int col0 = n_t * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < p.num_kb; kb += C::kKbPerStage) {
           if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
           // One expect_tx per stage, posted locally by the even CTA for the bytes of BOTH CTAs; the
           // partner only issues its loads, whose completions are counted on the even CTA's barrier.
           // (Its bytes can only arrive after the stage's previous phase has completed, because its
           // own `empty` wait above is released by a commit that follows that completion.)
-          const uint32_t a_dst = smem_base + s * C::kStageBytes, b_dst = a_dst + A_STAGE_BYTES;
-          if (rank == 0) {
-            const uint32_t full = bar_full + 8 * s;
-            mbar_expect_tx(full, 2 * (A_STAGE_BYTES + C::kBHalfBytes));
-            tma_load_4d(a_dst, &map_a, full, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
-            if (B_MN) {
+          // Stage layout: [A kb][A kb+1][B kb][B kb+1]; a k-block past the end of K is zero-filled.
+          const uint32_t stage = smem_base + s * C::kStageBytes;
+          const uint32_t full = rank == 0 ? bar_full + 8 * s : full_pair0 + 8 * s;
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * C::kStageBytes);
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_4d(b_dst + j * (BK * 128), &map_b, full, col0 + 32 * j, kb * BK, bi * p.b_bi, bo * p.b_bo);
-            } else {
-              tma_load_4d(b_dst, &map_b, full, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
-            }
-          } else {
-            const uint32_t full_pair = full_pair0 + 8 * s;  // the even CTA's barrier (shared::cluster address)
-            tma_load_4d_pair(a_dst, &map_a, full_pair, kb * BK, row0, bi * p.a_bi, bo * p.a_bo);
-            if (B_MN) {
+          for (int h = 0; h < C::kKbPerStage; ++h) {
+            const uint32_t a_dst = stage + h * A_STAGE_BYTES;
+            const uint32_t b_dst = stage + C::kKbPerStage * A_STAGE_BYTES + h * C::kBHalfBytes;
+            const int k0 = (kb + h) * BK;
+            if (rank == 0) {
+              tma_load_4d(a_dst, &map_a, full, k0, row0, bi * p.a_bi, bo * p.a_bo);
+              if (B_MN) {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_4d_pair(b_dst + j * (BK * 128), &map_b, full_pair, col0 + 32 * j, kb * BK, bi * p.b_bi,
-                                 bo * p.b_bo);
+                for (int j = 0; j < BN / 64; ++j)
+                  tma_load_4d(b_dst + j * (BK * 128), &map_b, full, col0 + 32 * j, k0, bi * p.b_bi, bo * p.b_bo);
+              } else {
+                tma_load_4d(b_dst, &map_b, full, k0, col0, bi * p.b_bi, bo * p.b_bo);
+              }
             } else {
-              tma_load_4d_pair(b_dst, &map_b, full_pair, kb * BK, col0, bi * p.b_bi, bo * p.b_bo);
+              tma_load_4d_pair(a_dst, &map_a, full, k0, row0, bi * p.a_bi, bo * p.a_bo);
+              if (B_MN) {
+#pragma unroll
+                for (int j = 0; j < BN / 64; ++j)
+                  tma_load_4d_pair(b_dst + j * (BK * 128), &map_b, full, col0 + 32 * j, k0, bi * p.b_bi, bo * p.b_bo);
+              } else {
+                tma_load_4d_pair(b_dst, &map_b, full, k0, col0, bi * p.b_bi, bo * p.b_bo);
+              }
             }
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
@@ -606,9 +614,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       constexpr uint32_t kStage16 = C::kStageBytes >> 4;
       constexpr uint32_t kAStep = (UMMA_K * 4) >> 4;
       constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);
+      constexpr uint32_t kBOff = C::kKbPerStage * A_STAGE_BYTES;
       const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128);
-      const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + A_STAGE_BYTES, BK * 128, 512, kLayoutSw128Base32)
-                                    : make_smem_desc(smem_base + A_STAGE_BYTES, 16, 1024, kLayoutSw128);
+      const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + kBOff, BK * 128, 512, kLayoutSw128Base32)
+                                    : make_smem_desc(smem_base + kBOff, 16, 1024, kLayoutSw128);
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -618,14 +627,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 2u))) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = 0; kb < p.num_kb; kb += C::kKbPerStage) {
           if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 4u))) break;
           tc_fence_after();
           const uint64_t a_d = a_desc0 + (uint32_t)s * kStage16, b_d = b_desc0 + (uint32_t)s * kStage16;
           const uint32_t first = kb > 0 ? 1u : 0u;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk)
-            umma_tf32_pair(d_tmem, a_d + kk * kAStep, b_d + kk * kBStep, idesc, kk > 0 ? 1u : first);
+          for (int h = 0; h < C::kKbPerStage; ++h) {
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+              umma_tf32_pair(d_tmem, a_d + h * (A_STAGE_BYTES >> 4) + kk * kAStep,
+                             b_d + h * (C::kBHalfBytes >> 4) + kk * kBStep, idesc, (h > 0 || kk > 0) ? 1u : first);
+          }
           // the stage is reusable in both CTAs once these MMAs have read it
           umma_commit_pair_both(bar_empty + 8 * s, 3);
           if (++s == kStages) { s = 0; ph ^= 1; }

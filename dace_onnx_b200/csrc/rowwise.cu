@@ -208,12 +208,15 @@ layernorm_warp_vec_kernel(const float *__restrict__ x, const float *__restrict__
   }
   const float var = warp_sum(q) / (float)len;  // ReduceMean
   const float sd = sqrtf(var + eps);           // Add eps, Sqrt
+  // Div: one IEEE reciprocal per row, then a multiply per element. x * (1/sd) differs from x / sd by
+  // at most one ulp; a per-element IEEE division would make this kernel instruction-bound.
+  const float inv = 1.0f / sd;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = lane + 32 * i;
     if (c < nvec) {
       float4 o;
-      o.x = v[i].x / sd; o.y = v[i].y / sd; o.z = v[i].z / sd; o.w = v[i].w / sd;  // Div
+      o.x = v[i].x * inv; o.y = v[i].y * inv; o.z = v[i].z * inv; o.w = v[i].w * inv;
       if (gamma) {
         const float4 g = *reinterpret_cast<const float4 *>(gamma + 4 * c);
         o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;  // Mul
