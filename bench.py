@@ -244,7 +244,7 @@ def run_b200(args, wl):
     alg_bytes = sum(4 * (t_tok * k + n * k + t_tok * n) for n, k in gemm_shapes) / len(gemm_shapes)
     traffic = 0.83 * alg_bytes
     achieved = g[1] / g[0] / 1e12
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel<256, K-major, TF32> (dense projections)",
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<256, K-major> (TF32 dense projections, CTA pairs)",
                 "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                 "peak_source": "%s bf16 sustained / 2 (TF32 runs at half the bf16 rate)" % peaks["source"],
                 "avg_launch_ms": g[0] * 1e3 / max(g[3], 1), "traffic": traffic,
