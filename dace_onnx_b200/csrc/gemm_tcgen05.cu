@@ -10,9 +10,10 @@
 //               two or four warps per lane quarter), apply the fused epilogue (bias / ReLU / erf-Gelu /
 //               residual / scale) and store with 256-bit vector stores, each thread writing whole
 //               32-byte sectors of its row (128-bit / scalar stores when Y is less aligned);
-//   last 4 warps (3xTF32 mode only) split warps: rewrite each landed stage in place as
-//               hi = tf32(x) and write lo = tf32(x - hi) beside it, so that the issuer can run
-//               lo*hi + hi*lo + hi*hi into the same fp32 accumulator (fp32-accurate products).
+//   last 8 warps (3xTF32 mode only) split warps: split each landed stage into hi = tf32(x) and
+//               lo = tf32(x - hi) -- A into TMEM (the MMAs then read A from TMEM), B in shared
+//               memory -- so that the issuer can run lo*hi + hi*lo + hi*hi into the same fp32
+//               accumulator (fp32-accurate products).
 // Two TMEM accumulators alternate so that the epilogue of tile i overlaps the MMAs of tile i+1.
 //
 // Every mbarrier wait is bounded by a cycle budget; on expiry the CTA sets a bit in the device
@@ -60,8 +61,8 @@ struct GemmParams {
   unsigned *status;
 };
 
-// k-blocks per in-core accumulation chunk in 3xTF32 mode (2 x 32 = 64 values of K, 24 MMAs).
-constexpr int kSplitChunkKb = 2;
+// k-blocks per in-core accumulation chunk in 3xTF32 mode (4 x 32 = 128 values of K, 48 MMAs).
+constexpr int kSplitChunkKb = 4;
 
 __device__ __forceinline__ void ld_global_v8(const float *p, float *v) {
   asm volatile("ld.global.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -172,16 +173,22 @@ __device__ __forceinline__ void finish_pixel32(const GemmParams &p, const float 
 template <int BN, bool SPLIT3>
 struct Cfg {
   static constexpr int kBStageBytes = BN * BK * 4;
-  static constexpr int kStageBytes = (A_STAGE_BYTES + kBStageBytes) * (SPLIT3 ? 2 : 1);
-  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
-  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators; BN is a power of two
+  // 3xTF32: stage = [A raw | B -> B_hi in place | B_lo]; A's hi / lo halves live in TMEM, 64 columns
+  // per stage behind the two accumulators, which bounds the stage count: 2*BN + 64*stages <= 512.
+  static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes * (SPLIT3 ? 2 : 1);
+  static constexpr int kStagesSmem = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
+  static constexpr int kStagesTmem = (512 - 2 * BN) / 64;
+  static constexpr int kStages = (SPLIT3 && kStagesTmem < kStagesSmem) ? kStagesTmem : kStagesSmem;
+  static constexpr int kTmemCols = SPLIT3 ? 512 : (2 * BN < 32 ? 32 : 2 * BN);  // two accumulators (+ A halves)
+  static constexpr int kASplitCol0 = 2 * BN;  // first TMEM column of the A hi/lo stages
   // Epilogue warps: four per 64 accumulator columns, i.e. 2 (BN=64), 2 (BN=128, 3xTF32 keeps its
   // column sums in registers), 4 warps per TMEM lane quarter for the wide TF32 tiles, whose erf-Gelu
   // epilogue would otherwise take as long as the tile's MMAs.
   static constexpr int kWarpsPerQuarter = (BN >= 128 && !SPLIT3) ? 4 : 2;
   static constexpr int kEpilogueWarps = 4 * kWarpsPerQuarter;
   static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
-  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + (SPLIT3 ? 4 : 0));
+  static constexpr int kSplitWarps = SPLIT3 ? 8 : 0;  // two per TMEM lane quarter
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kSplitWarps);
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr int kColsPerWarp = BN / kWarpsPerQuarter;
 };
@@ -213,7 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
-      mbar_init(bar_split + 8 * s, 128);
+      mbar_init(bar_split + 8 * s, 32 * (C::kSplitWarps > 0 ? C::kSplitWarps : 1));
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
@@ -312,7 +319,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128);
       const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + A_STAGE_BYTES, BK * 128, 512, kLayoutSw128Base32)
                                     : make_smem_desc(smem_base + A_STAGE_BYTES, 16, 1024, kLayoutSw128);
-      constexpr uint32_t kALo16 = (A_STAGE_BYTES + C::kBStageBytes) >> 4;  // hi -> lo copy of the same operand
+      constexpr uint32_t kBLo16 = C::kBStageBytes >> 4;  // B_hi -> B_lo of the same stage
       const int chunk = SPLIT3 ? kSplitChunkKb : p.num_kb;
       int s = 0;
       uint32_t ph = 0;
@@ -335,9 +342,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int kk = 0; kk < BK / UMMA_K; ++kk) {
               const uint32_t accumulate = kk > 0 ? 1u : first;
               if (SPLIT3) {
-                umma_tf32(d_tmem, a_hi + kALo16 + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);  // lo * hi
-                umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kALo16 + kk * kBStep, idesc, 1u);          // hi * lo
-                umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, 1u);                   // hi * hi
+                // A operand from TMEM: 32 columns of hi then 32 of lo per stage, 8 columns per k-step
+                const uint32_t a_hi_t = tmem_base + C::kASplitCol0 + (uint32_t)s * 64 + kk * UMMA_K;
+                umma_tf32_ts(d_tmem, a_hi_t + 32, b_hi + kk * kBStep, idesc, accumulate);      // lo * hi
+                umma_tf32_ts(d_tmem, a_hi_t, b_hi + kBLo16 + kk * kBStep, idesc, 1u);          // hi * lo
+                umma_tf32_ts(d_tmem, a_hi_t, b_hi + kk * kBStep, idesc, 1u);                   // hi * hi
               } else {
                 umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);
               }
@@ -396,12 +405,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < C::kColsPerWarp; c += 32) {
-            uint32_t v[32];
-            tmem_ld32(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
+          for (int c = 0; c < C::kColsPerWarp; c += 16) {  // 16 columns at a time: keeps registers for `sum`
+            uint32_t v[16];
+            tmem_ld16(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sum[c + j] += __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) sum[c + j] += __uint_as_float(v[j]);
           }
           tc_fence_before();
           mbar_arrive(bar_tempty + 8 * acc);
@@ -433,20 +442,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (SPLIT3) {
     // ------------------------------- 3xTF32 split warps -------------------------------
-    const int t = threadIdx.x - 32 * C::kSplitWarp0;  // 0..127
+    // Each landed stage is split into hi = tf32(x) and lo = tf32(x - hi).
+    //  * A: thread = row (the warp's TMEM lane quarter). The row's 32 values are read from the
+    //    128B-swizzled tile (16-byte chunk c of row r sits at chunk c ^ (r % 8)) and the two halves
+    //    are written to TMEM, where the MMAs read their A operand: A costs shared memory one read.
+    //  * B: split elementwise in shared memory (hi in place, lo beside it); the swizzled placement
+    //    of each chunk is preserved by writing at the same offset.
+    // Shared-memory bandwidth bounds this mode (tile traffic + the MMAs' B reads), hence A in TMEM.
+    const int t = threadIdx.x - 32 * C::kSplitWarp0;  // 0..255
+    const int quarter = warp & 3;
+    const int colhalf = (warp - C::kSplitWarp0) >> 2;  // which 16 of the row's 32 values this warp splits
+    const int row = quarter * 32 + lane;
+    const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kASplitCol0 + colhalf * 16;
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < p.num_kb; ++kb) {
         if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 16u))) break;
-        // A and B tiles are contiguous ([A | B | A_lo | B_lo]); the split is elementwise, so the
-        // swizzled placement of each 16-byte chunk is preserved by writing at the same offset.
-        float4 *src = reinterpret_cast<float4 *>(smem + (size_t)s * C::kStageBytes);
-        float4 *dst_lo = reinterpret_cast<float4 *>(smem + (size_t)s * C::kStageBytes + A_STAGE_BYTES + C::kBStageBytes);
-        constexpr int kVecs = (A_STAGE_BYTES + C::kBStageBytes) / 16;
+        uint8_t *stage = smem + (size_t)s * C::kStageBytes;
+        {
+          const float4 *arow = reinterpret_cast<const float4 *>(stage + row * 128);
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float4 x = arow[(colhalf * 4 + c) ^ (row & 7)];
+            const float h0 = to_tf32_rna(x.x), h1 = to_tf32_rna(x.y), h2 = to_tf32_rna(x.z), h3 = to_tf32_rna(x.w);
+            hi[4 * c + 0] = __float_as_uint(h0); hi[4 * c + 1] = __float_as_uint(h1);
+            hi[4 * c + 2] = __float_as_uint(h2); hi[4 * c + 3] = __float_as_uint(h3);
+            lo[4 * c + 0] = __float_as_uint(to_tf32_rna(x.x - h0)); lo[4 * c + 1] = __float_as_uint(to_tf32_rna(x.y - h1));
+            lo[4 * c + 2] = __float_as_uint(to_tf32_rna(x.z - h2)); lo[4 * c + 3] = __float_as_uint(to_tf32_rna(x.w - h3));
+          }
+          tmem_st16(a_lane + (uint32_t)s * 64, hi);
+          tmem_st16(a_lane + (uint32_t)s * 64 + 32, lo);
+        }
+        float4 *src = reinterpret_cast<float4 *>(stage + A_STAGE_BYTES);
+        float4 *dst_lo = reinterpret_cast<float4 *>(stage + A_STAGE_BYTES + C::kBStageBytes);
+        constexpr int kVecs = C::kBStageBytes / 16;
 #pragma unroll 4
-        for (int i = t; i < kVecs; i += 128) {
+        for (int i = t; i < kVecs; i += 32 * C::kSplitWarps) {
           const float4 x = src[i];
           float4 hi, lo;
           hi.x = to_tf32_rna(x.x); hi.y = to_tf32_rna(x.y); hi.z = to_tf32_rna(x.z); hi.w = to_tf32_rna(x.w);
@@ -455,7 +489,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           src[i] = hi;
           dst_lo[i] = lo;
         }
-        // Make the generic-proxy writes visible to the tensor core (async proxy) before signalling.
+        // Publish: TMEM stores complete, generic-proxy shared-memory writes visible to the tensor core.
+        tmem_st_wait();
+        tc_fence_before();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_arrive(bar_split + 8 * s);
         if (++s == kStages) { s = 0; ph ^= 1; }
