@@ -71,6 +71,10 @@ def test_transposes(cuda):
     assert torch.equal(ops.transpose_0213(x.cuda()).cpu(), x.permute(0, 2, 1, 3).contiguous())
     w = torch.randn(3, 70, 45, generator=torch.Generator().manual_seed(17))
     assert torch.equal(ops.transpose_last2(w.cuda()).cpu(), w.transpose(-1, -2).contiguous())
+    # multiples of four take the 64 x 64 vectorised tiles: ragged tile edges and exact tiles
+    for shape, seed in (((3, 68, 44), 18), ((2, 128, 192), 19), ((5, 4, 260), 20), ((1, 1000, 8), 21)):
+        w = torch.randn(*shape, generator=torch.Generator().manual_seed(seed))
+        assert torch.equal(ops.transpose_last2(w.cuda()).cpu(), w.transpose(-1, -2).contiguous())
 
 
 def test_binary_linearity_at_full_size(cuda):
