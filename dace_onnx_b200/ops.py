@@ -172,6 +172,14 @@ def attention_views(q, k, v, out, scale, math_mode=None):
     return True
 
 
+def conv2d_workspace_bytes(x_shape, w_shape, pads=(0, 0, 0, 0), strides=(1, 1), math_mode=None):
+    """Device scratch b200_conv2d_f32 wants for this convolution (0 when it runs without any)."""
+    N, C, H, Wd = x_shape
+    M, _, KH, KW = w_shape
+    d = ConvDesc(N, C, H, Wd, M, KH, KW, pads[0], pads[1], strides[0], strides[1], EPI_NONE, _math(math_mode))
+    return int(_lib.load().b200_conv2d_workspace_bytes(ctypes.byref(d)))
+
+
 def conv2d(X, W, B=None, out=None, *, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), group=1, relu=False,
            workspace=None, math_mode=None):
     """ONNXConv, NCHW / OIHW, group 1, dilation 1, symmetric pads [top, left, bottom, right]."""
@@ -368,6 +376,33 @@ def transpose_0213(x, out=None):
     if out is None:
         out = torch.empty((d0, d2, d1, d3), device=x.device, dtype=torch.float32)
     check(_lib.load().b200_transpose_0213_f32(_stream(), _ptr(x), _ptr(out), d0, d1, d2, d3))
+    return out
+
+
+_ONES = {}
+
+
+def permute(x, perm, out=None):
+    """ONNXTranspose with an arbitrary perm (rank <= 8): the strided elementwise kernel reads the input
+    through permuted strides and multiplies by a broadcast 1.0, which returns every value unchanged."""
+    x = _contig(x, "data")
+    n = x.dim()
+    perm = [int(p) % n for p in perm]
+    if sorted(perm) != list(range(n)):
+        raise ValueError("permute: %s is not a permutation of %d axes" % (perm, n))
+    if n > 8:
+        raise NotImplementedError("permute: rank > 8")
+    xv = x.permute(perm)  # a view: no data moves here
+    if out is None:
+        out = torch.empty(tuple(xv.shape), device=x.device, dtype=torch.float32)
+    elif tuple(out.shape) != tuple(xv.shape) or not out.is_contiguous():
+        raise ValueError("permute: out must be contiguous with shape %s" % (tuple(xv.shape),))
+    one = _ONES.get(x.device)
+    if one is None:
+        one = _ONES[x.device] = torch.ones((), device=x.device, dtype=torch.float32)
+    arr = ctypes.c_int64 * max(n, 1)
+    check(_lib.load().b200_binary_f32(_stream(), MUL, _ptr(xv), _ptr(one), _ptr(out), n, arr(*xv.shape),
+                                      arr(*xv.stride()), arr(*([0] * n))))
     return out
 
 
