@@ -140,8 +140,7 @@ def run_reference(args, wl):
 def run_b200(args, wl):
     import torch.distributed as dist
     from dace_onnx_b200 import _lib, sharding
-    from dace_onnx_b200.encoder import BertEncoderB200
-    from oracle import pure_oracle as po  # seeded weight generator shared with the CPU baseline
+    from dace_onnx_b200.encoder import BertEncoderB200, synthetic_layer_params
 
     layers, hidden, heads, ffn, batch, seq, mode = WORKLOADS[wl]
     if not torch.cuda.is_available():
@@ -155,7 +154,7 @@ def run_b200(args, wl):
     _lib.load()
 
     # replicated weights from the same seeds on every rank (no broadcast needed)
-    params = [po.make_bert_layer_params(hidden, ffn, seed=100 + i) for i in range(layers)]
+    params = [synthetic_layer_params(hidden, ffn, seed=100 + i) for i in range(layers)]
     enc = BertEncoderB200(params, heads, device=device, math_mode=mode, micro_batch=args.micro_batch)
     del params
     lo, hi = sharding.shard_bounds(batch, world, rank)
@@ -365,7 +364,54 @@ def kernel_cases(device):
             return fn, 2 * n * hw * hw * m * c * 9, 4 * (x.numel() + y.numel()), "tensor"
         return make
 
+    def frontdoor_bert_layer(b, s, hidden, heads, ffn, mode):
+        # transformers.BertLayer exported to ONNX and run through the graph front door (49 nodes -> 6 fused)
+        def make():
+            from transformers import BertConfig, BertLayer
+            from dace_onnx_b200.torch_module import B200Module
+            torch.manual_seed(0)
+            cfg = BertConfig(hidden_size=hidden, num_attention_heads=heads, intermediate_size=ffn,
+                             hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+            cfg._attn_implementation = "eager"
+            mod = B200Module(BertLayer(cfg).eval(), dummy_inputs=(torch.zeros(b, s, hidden),), math_mode=mode)
+            x = rn(b, s, hidden)
+            t = b * s
+            flops = 2 * t * hidden * (4 * hidden + 2 * ffn) + 4 * b * heads * s * s * (hidden // heads)
+            return (lambda: mod(x)), flops, 0, "tensor"
+        return make
+
+    def encoder_bert_layer(b, s, hidden, heads, ffn, mode):
+        # the hand-written runner on the same layer shape, for comparison with the front door
+        def make():
+            from dace_onnx_b200.encoder import BertEncoderB200, synthetic_layer_params
+            enc = BertEncoderB200([synthetic_layer_params(hidden, ffn, 0)], heads, device=str(device),
+                                  math_mode=mode, micro_batch=b)
+            x = rn(b, s, hidden)
+            y = torch.empty_like(x)
+            t = b * s
+            flops = 2 * t * hidden * (4 * hidden + 2 * ffn) + 4 * b * heads * s * s * (hidden // heads)
+            return (lambda: enc.forward_device(x, out=y)), flops, 0, "tensor"
+        return make
+
+    def frontdoor_mlp_c1(cuda_graph=False):
+        # configuration 1: Linear 784-120-32-10 + ReLU + LogSoftmax, batch 4096, exported and run from the graph
+        def make():
+            from dace_onnx_b200.torch_module import B200Module
+            torch.manual_seed(0)
+            net = torch.nn.Sequential(torch.nn.Linear(784, 120), torch.nn.ReLU(), torch.nn.Linear(120, 32),
+                                      torch.nn.ReLU(), torch.nn.Linear(32, 10), torch.nn.LogSoftmax(dim=1)).eval()
+            mod = B200Module(net, dummy_inputs=(torch.zeros(4096, 784),), math_mode="fp32x3", cuda_graph=cuda_graph)
+            x = rn(4096, 784)
+            if cuda_graph:  # the serving pattern: fill the captured input buffer in place, replay
+                mod(x)
+                x = mod.onnx_model.static_inputs(x.shape)[0].copy_(x)
+            return (lambda: mod(x)), 2 * 4096 * (784 * 120 + 120 * 32 + 32 * 10), 13.40e6, "hbm"
+        return make
+
     return {
+        "frontdoor_bert_large_layer_tf32": frontdoor_bert_layer(64, 384, 1024, 16, 4096, "tf32"),
+        "encoder_bert_large_layer_tf32": encoder_bert_layer(64, 384, 1024, 16, 4096, "tf32"),
+        "frontdoor_mlp_c1": frontdoor_mlp_c1(), "frontdoor_mlp_c1_cudagraph": frontdoor_mlp_c1(True),
         "conv_c2_fp32x3": conv(256, 64, 56, 64, "fp32x3"), "conv_c2_tf32": conv(256, 64, 56, 64, "tf32"),
         "softmax_c4": softmax_c4, "layernorm_c4": layernorm_c4,
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),

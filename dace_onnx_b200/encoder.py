@@ -25,6 +25,22 @@ from . import ops
 from ._lib import EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_SCALE
 
 
+def synthetic_layer_params(hidden, ffn, seed, std=0.02):
+    """Random-init weights of one encoder layer for benchmarks: matrices ~ N(0, std^2) from a seeded CPU
+    generator (the same values on every rank that uses the same seed), biases 0, LayerNorm gamma 1 / beta 0."""
+    g = torch.Generator().manual_seed(int(seed))
+    p = {}
+    for key, shape in (("wq", (hidden, hidden)), ("wk", (hidden, hidden)), ("wv", (hidden, hidden)),
+                       ("wo", (hidden, hidden)), ("wi", (ffn, hidden)), ("wo2", (hidden, ffn))):
+        p[key] = torch.randn(*shape, generator=g, dtype=torch.float32) * std
+    for key, n in (("bq", hidden), ("bk", hidden), ("bv", hidden), ("bo", hidden), ("bi", ffn), ("bo2", hidden),
+                   ("ln1_b", hidden), ("ln2_b", hidden)):
+        p[key] = torch.zeros(n, dtype=torch.float32)
+    p["ln1_g"] = torch.ones(hidden, dtype=torch.float32)
+    p["ln2_g"] = torch.ones(hidden, dtype=torch.float32)
+    return p
+
+
 class BertEncoderB200:
     """N identical-shape BERT encoder layers on one GPU.
 

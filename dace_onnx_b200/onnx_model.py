@@ -271,6 +271,36 @@ class _Plan:
         return outs
 
 
+class _GraphReplay:
+    """A plan captured into a CUDA graph: one launch per call instead of one per node. The captured kernels
+    read input buffers owned by the replay and write output buffers that were current at capture time: inputs are
+    first copied into those buffers (unless the caller passes the buffers themselves, see
+    ONNXModelB200.static_inputs), and the returned tensors are overwritten by the next call."""
+
+    def __init__(self, plan: _Plan, inputs: Sequence[torch.Tensor]):
+        self.plan = plan
+        self.inputs = [t.to(plan.device, copy=True) for t in inputs]
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream(device=plan.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):  # every lazily created scratch buffer and per-device table exists before the capture
+                plan.run(self.inputs)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(plan.device)
+        _lib.device_status()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.outputs = plan.run(self.inputs)
+
+    def __call__(self, inputs: Sequence[torch.Tensor]):
+        for mine, given in zip(self.inputs, inputs):
+            if mine.data_ptr() != given.data_ptr():
+                mine.copy_(given, non_blocking=True)
+        self.graph.replay()
+        return self.outputs
+
+
 class ONNXModelB200:
     """Loads an ONNX model and executes it on one B200.
 
@@ -282,9 +312,12 @@ class ONNXModelB200:
                  With False every exported node runs as its own kernel, the way the reference's per-node
                  expansion does.
     :param math_mode: "fp32x3" (fp32-accurate, default), "tf32" or "fp32" for the contractions.
+    :param cuda_graph: capture each plan into a CUDA graph on its first call and replay it afterwards (for
+                 graphs of many small kernels, where launch latency dominates). The returned tensors are then
+                 owned by the model and overwritten by its next call with the same input shapes.
     """
 
-    def __init__(self, name, model, cuda=True, fuse=True, math_mode=None, device=None):
+    def __init__(self, name, model, cuda=True, fuse=True, math_mode=None, device=None, cuda_graph=False):
         if not cuda:
             raise ValueError("ONNXModelB200 runs on a CUDA device only (cuda=False is not available)")
         if isinstance(model, onnx_wire.Model):
@@ -304,6 +337,8 @@ class ONNXModelB200:
                 self.model.opset)
         _lib.load()  # fail now, not at the first call, when the CUDA library is missing
         self._plans: Dict[tuple, _Plan] = {}
+        self.cuda_graph = bool(cuda_graph)
+        self._replays: Dict[tuple, _GraphReplay] = {}
 
     @property
     def input_names(self):
@@ -322,6 +357,14 @@ class ONNXModelB200:
                 p = _Plan(self.model, key, self.device, self.fuse, self.math_mode)
             self._plans[key] = p
         return p
+
+    def static_inputs(self, *shapes):
+        """With cuda_graph=True: the input buffers the captured graph of these shapes reads (after its first call).
+        Filling them in place and passing them to the call avoids the copy of the inputs."""
+        key = tuple(tuple(int(d) for d in s) for s in shapes)
+        if key not in self._replays:
+            raise KeyError("no captured graph for input shapes %s yet" % (key,))
+        return list(self._replays[key].inputs)
 
     def _bind(self, args, kwargs):
         names = self.input_names
@@ -356,5 +399,13 @@ class ONNXModelB200:
         (cleaned) name. Returns the output as a CUDA tensor, or a tuple when there are several."""
         inputs = self._bind(args, kwargs)
         with torch.cuda.device(self.device):
-            outs = self.plan(*[t.shape for t in inputs]).run(inputs)
+            plan = self.plan(*[t.shape for t in inputs])
+            if self.cuda_graph:
+                key = tuple(tuple(t.shape) for t in inputs)
+                replay = self._replays.get(key)
+                if replay is None:
+                    replay = self._replays[key] = _GraphReplay(plan, inputs)
+                outs = replay(inputs)
+            else:
+                outs = plan.run(inputs)
         return outs[0] if len(outs) == 1 else tuple(outs)

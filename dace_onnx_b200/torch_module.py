@@ -42,10 +42,10 @@ class B200Module(torch.nn.Module):
     """:param module: the model to run (put in eval mode for the export).
     :param dummy_inputs: example inputs to export with now; otherwise the first call's inputs are used.
     :param cuda: must stay True (there is no CPU execution).
-    :param fuse, math_mode: see ONNXModelB200."""
+    :param fuse, math_mode, cuda_graph: see ONNXModelB200."""
 
     def __init__(self, module, dummy_inputs=None, cuda=True, training=False, fuse=True, math_mode=None,
-                 sdfg_name=None):
+                 sdfg_name=None, cuda_graph=False):
         super().__init__()
         if training:
             raise NotImplementedError("B200Module runs inference only")
@@ -55,6 +55,7 @@ class B200Module(torch.nn.Module):
         self.sdfg_name = sdfg_name or type(module).__name__
         self.fuse = fuse
         self.math_mode = math_mode
+        self.cuda_graph = cuda_graph
         self.onnx_model = None
         if dummy_inputs is not None:
             self._initialize(dummy_inputs if isinstance(dummy_inputs, (tuple, list)) else (dummy_inputs,))
@@ -65,7 +66,8 @@ class B200Module(torch.nn.Module):
         cpu_model = self.model.to("cpu")
         data = export_onnx(cpu_model, tuple(t.detach().to("cpu") for t in inputs))
         self.model.train(was_training)
-        self.onnx_model = ONNXModelB200(self.sdfg_name, data, cuda=True, fuse=self.fuse, math_mode=self.math_mode)
+        self.onnx_model = ONNXModelB200(self.sdfg_name, data, cuda=True, fuse=self.fuse, math_mode=self.math_mode,
+                                        cuda_graph=self.cuda_graph)
 
     def forward(self, *inputs):
         if self.onnx_model is None:

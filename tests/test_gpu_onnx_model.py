@@ -115,3 +115,22 @@ def test_b200_module_live_export_with_fused_attention(cuda):
         plan = mod.onnx_model.plan((4, 128, 256))
         assert plan.ir.op_histogram() == {"B200SelfAttention": 1, "B200Gemm": 3, "B200LayerNorm": 2}
         close(mod(x.cuda()), out, 0, 0)              # same plan, same buffers, same result
+
+
+@pytest.mark.parametrize("name", ["mlp", "bert_layer", "conv_stack"])
+def test_cuda_graph_replay_equals_eager(name, cuda):
+    g = golden("onnx_" + name)
+    x = torch.from_numpy(g["x"]).cuda()
+    eager = ONNXModelB200(name, _path(name))(x)
+    model = ONNXModelB200(name, _path(name), cuda_graph=True)
+    y1 = model(x).clone()                      # first call captures
+    y2 = model(x).clone()                      # replay, same input address
+    y3 = model(x.clone()).clone()              # replay after a copy into the captured input buffer
+    assert torch.equal(y1, eager) and torch.equal(y2, eager) and torch.equal(y3, eager)
+    z = model(torch.zeros_like(x)).clone()
+    assert not torch.equal(z, eager)
+    assert torch.equal(model(x), eager)
+    assert torch.equal(x.cpu(), torch.from_numpy(g["x"]))      # the caller's tensors are never written
+    buf = model.static_inputs(x.shape)[0]
+    buf.copy_(x)
+    assert torch.equal(model(buf), eager)
