@@ -61,8 +61,20 @@ extern "C" B200_API int b200_device_status(void) {
   return B200_OK;
 }
 
-extern "C" B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
-                             const float *bias, const float *residual, float *Y) {
+namespace {
+// numpy-style "[batch..., M, K] @ [K, N]" with a dense batch is one tall GEMM.
+void flatten_dense_batch(b200_gemm_desc &d) {
+  const int64_t batch = d.batch_outer * d.batch_inner;
+  if (batch > 1 && d.b_stride_outer == 0 && d.b_stride_inner == 0 && d.a_stride_inner == d.M * d.lda &&
+      d.y_stride_inner == d.M * d.ldy && (d.batch_outer == 1 || (d.a_stride_outer == d.batch_inner * d.a_stride_inner &&
+                                                                  d.y_stride_outer == d.batch_inner * d.y_stride_inner))) {
+    d.M *= batch;
+    d.batch_outer = d.batch_inner = 1;
+  }
+}
+
+int gemm_entry(void *stream, const b200_gemm_desc *desc, const float *A, const float *B, const float *bias,
+               const float *residual, float *Y, void *workspace, size_t workspace_bytes) {
   cudaStream_t st = (cudaStream_t)stream;
   if (!desc) return fail(B200_EINVAL, "gemm: null descriptor");
   b200_gemm_desc d = *desc;
@@ -87,19 +99,32 @@ extern "C" B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, 
   if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
     return fail(B200_EINVAL, "gemm: unknown math mode %d", d.math_mode);
 
-  // numpy-style "[batch..., M, K] @ [K, N]" with a dense batch is one tall GEMM.
-  const int64_t batch = d.batch_outer * d.batch_inner;
-  if (batch > 1 && d.b_stride_outer == 0 && d.b_stride_inner == 0 && d.a_stride_inner == d.M * d.lda &&
-      d.y_stride_inner == d.M * d.ldy && (d.batch_outer == 1 || (d.a_stride_outer == d.batch_inner * d.a_stride_inner &&
-                                                                  d.y_stride_outer == d.batch_inner * d.y_stride_inner))) {
-    d.M *= batch;
-    d.batch_outer = d.batch_inner = 1;
-  }
+  flatten_dense_batch(d);
 
   // Tensor-core path whenever TMA can address the operands; the CUDA-core kernel otherwise
   // (and when the caller asks for plain fp32 arithmetic).
-  if (d.math_mode != B200_MATH_FP32 && gemm_tc_supported(d, A, B, Y)) return gemm_tc(st, d, A, B, bias, residual, Y);
+  if (d.math_mode != B200_MATH_FP32 && gemm_tc_supported(d, A, B, Y))
+    return gemm_tc(st, d, A, B, bias, residual, Y, workspace, workspace_bytes);
   return gemm_simt(st, d, A, B, bias, residual, Y);
+}
+}  // namespace
+
+extern "C" B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
+                             const float *bias, const float *residual, float *Y) {
+  return gemm_entry(stream, desc, A, B, bias, residual, Y, nullptr, 0);
+}
+
+extern "C" B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_desc *desc) {
+  if (!desc || desc->M <= 0 || desc->N <= 0 || desc->K <= 0 || desc->batch_outer <= 0 || desc->batch_inner <= 0) return 0;
+  b200_gemm_desc d = *desc;
+  flatten_dense_batch(d);
+  return gemm_tc_workspace_bytes(d);
+}
+
+extern "C" B200_API int b200_gemm_ws_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
+                                const float *bias, const float *residual, float *Y, void *workspace,
+                                size_t workspace_bytes) {
+  return gemm_entry(stream, desc, A, B, bias, residual, Y, workspace, workspace_bytes);
 }
 
 extern "C" B200_API int b200_attention_supported(const b200_attention_desc *desc, const float *Q, const float *K,

@@ -42,8 +42,11 @@ int conv2d_simt(cudaStream_t st, const b200_conv_desc &d, const float *X, const 
 // tcgen05 path. `can_*` say whether the operands meet the TMA addressing rules (16-byte aligned
 // bases and row strides, K a multiple of 4); the launchers assume they do.
 bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, const float *Y);
+// `workspace` (optional, may be null): gemm_tc_workspace_bytes(d) bytes of device scratch; with it the 3xTF32
+// mode pre-splits B and runs the CTA-pair kernel.
+size_t gemm_tc_workspace_bytes(const b200_gemm_desc &d);
 int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
-            const float *residual, float *Y);
+            const float *residual, float *Y, void *workspace = nullptr, size_t workspace_bytes = 0);
 
 // Tensor-core convolution: NCHW -> NHWC and filter repack into the caller's workspace, then the
 // implicit GEMM. Supported for stride 1 and channel counts that are multiples of 4 (>= 16).

@@ -740,6 +740,279 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant of the 3xTF32 mode: a cluster of two CTAs computes a 256 x 128 tile with
+// tcgen05.mma.cta_group::2. B arrives already split (hi = tf32(B), lo = tf32(B - hi), written once per
+// call into the caller's workspace by split_tf32_kernel), so each CTA loads its 128 rows of raw A and
+// 64 of the 128 tile columns of B_hi and B_lo; its split warps only turn A into hi / lo halves in TMEM.
+// Per FLOP this halves the B operand reads of the tensor core and removes the B split from shared
+// memory, whose bandwidth bounds the single-CTA 3xTF32 kernel. Chunked accumulation as there: every
+// kSplitChunkKb k-blocks go to their own TMEM buffer and the epilogue warps sum the chunks in registers.
+// Barriers (same offsets in both CTAs):
+//   full[s]    own CTA: its TMA bytes of stage s            empty[s]  own CTA: multicast commit of the issuer
+//   split[s]   even CTA: one arrival per split warp of both CTAs (A halves of stage s are in TMEM)
+//   tfull[a]   own CTA: multicast commit                    tempty[a] even CTA: one arrival per epilogue warp of both
+// ---------------------------------------------------------------------------------------------
+struct Cfg3P {
+  static constexpr int BN = 128;
+  static constexpr int kBHalfBytes = (BN / 2) * BK * 4;                  // 8 KiB: 64 tile columns of one B half
+  static constexpr int kStageBytes = A_STAGE_BYTES + 2 * kBHalfBytes;    // A raw | B_hi | B_lo
+  static constexpr int kStages = 6;                                      // shared-memory ring (TMA runs this far ahead)
+  static constexpr int kSlots = 4;                                       // A hi/lo slots in TMEM (64 columns each)
+  static constexpr int kASplitCol0 = 2 * BN;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kEpilogueWarps = 8, kSplitWarps = 8;
+  static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kSplitWarps);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kColsPerWarp = BN / 2;
+};
+
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg3P::kThreads, 1)
+gemm_tc_pair3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bh,
+                     const __grid_constant__ CUtensorMap map_bl, const GemmParams p) {
+  using C = Cfg3P;
+  constexpr int kStages = C::kStages;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_split = bar_empty + 8 * kStages;  // one per TMEM slot
+  const uint32_t bar_tfull = bar_split + 8 * C::kSlots;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t rank = cluster_ctarank();
+  const int64_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int t = 0; t < C::kSlots; ++t) mbar_init(bar_split + 8 * t, 2 * C::kSplitWarps);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&s_tmem_base), C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int *abort_flag = &s_abort;
+  const int64_t num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;  // p.num_m_tiles counts 256-row pairs
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs, own barrier) -------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int n_t = (int)(tile % p.num_n_tiles);
+        const int m_t = (int)(tile / p.num_n_tiles);
+        const int row0 = (2 * m_t + (int)rank) * BM;
+        const int col0 = n_t * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
+          const uint32_t stage = smem_base + s * C::kStageBytes;
+          const uint32_t full = bar_full + 8 * s;
+          mbar_expect_tx(full, C::kStageBytes);
+          tma_load_4d(stage, &map_a, full, kb * BK, row0, 0, 0);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+              tma_load_4d(stage + A_STAGE_BYTES + j * (BK * 128), &map_bh, full, col0 + 32 * j, kb * BK, 0, 0);
+              tma_load_4d(stage + A_STAGE_BYTES + C::kBHalfBytes + j * (BK * 128), &map_bl, full, col0 + 32 * j,
+                          kb * BK, 0, 0);
+            }
+          } else {
+            tma_load_4d(stage + A_STAGE_BYTES, &map_bh, full, kb * BK, col0, 0, 0);
+            tma_load_4d(stage + A_STAGE_BYTES + C::kBHalfBytes, &map_bl, full, kb * BK, col0, 0, 0);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (even CTA only) -------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_pair(BN, B_MN);
+      constexpr uint32_t kStage16 = C::kStageBytes >> 4;
+      constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);
+      constexpr uint32_t kBLo16 = C::kBHalfBytes >> 4;
+      const uint64_t b_desc0 = B_MN ? make_smem_desc(smem_base + A_STAGE_BYTES, BK * 128, 512, kLayoutSw128Base32)
+                                    : make_smem_desc(smem_base + A_STAGE_BYTES, 16, 1024, kLayoutSw128);
+      int s = 0, slot = 0;
+      uint32_t slot_ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += kSplitChunkKb) {
+          if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort_flag, p.status, 2u))) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const int kb_end = kb0 + kSplitChunkKb < p.num_kb ? kb0 + kSplitChunkKb : p.num_kb;
+          for (int kb = kb0; kb < kb_end; ++kb) {
+            // both CTAs' split warps have put this k-block's A halves into TMEM slot `slot` (which also
+            // means both CTAs' loads of shared-memory stage s have landed)
+            if (!(ok = mbar_wait(bar_split + 8 * slot, slot_ph, abort_flag, p.status, 4u))) break;
+            tc_fence_after();
+            const uint64_t b_hi = b_desc0 + (uint32_t)s * kStage16;
+            const uint32_t first = kb > kb0 ? 1u : 0u;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              const uint32_t a_hi_t = tmem_base + C::kASplitCol0 + (uint32_t)slot * 64 + kk * UMMA_K;
+              umma_tf32_ts_pair(d_tmem, a_hi_t + 32, b_hi + kk * kBStep, idesc, kk > 0 ? 1u : first);  // lo * hi
+              umma_tf32_ts_pair(d_tmem, a_hi_t, b_hi + kBLo16 + kk * kBStep, idesc, 1u);                // hi * lo
+              umma_tf32_ts_pair(d_tmem, a_hi_t, b_hi + kk * kBStep, idesc, 1u);                         // hi * hi
+            }
+            umma_commit_pair_both(bar_empty + 8 * s, 3);
+            if (++s == kStages) s = 0;
+            if (++slot == C::kSlots) { slot = 0; slot_ph ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit_pair_both(bar_tfull + 8 * acc, 3);
+          if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp < C::kSplitWarp0) {
+    // ------------------------------- epilogue (both CTAs, own 128 rows) -------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int col0 = (ew >> 2) * C::kColsPerWarp;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int n_t = (int)(tile % p.num_n_tiles);
+      const int m_t = (int)(tile / p.num_n_tiles);
+      const int64_t m = (int64_t)(2 * m_t + (int)rank) * BM + quarter * 32 + lane;
+      const int64_t row_off = m * p.ldy;
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      float sum[C::kColsPerWarp];
+#pragma unroll
+      for (int j = 0; j < C::kColsPerWarp; ++j) sum[j] = 0.f;
+      for (int kb0 = 0; kb0 < p.num_kb; kb0 += kSplitChunkKb) {
+        if (!(ok = mbar_wait(bar_tfull + 8 * acc, acc_ph, abort_flag, p.status, 8u))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < C::kColsPerWarp; c += 16) {
+          uint32_t v[16];
+          tmem_ld16(lane_addr + (uint32_t)(acc * BN + col0 + c), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[c + j] += __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(bar_tempty + 8 * acc);
+          else mbar_arrive_cluster_relaxed(map_to_cta(bar_tempty + 8 * acc, 0));
+        }
+        if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int c = 0; c < C::kColsPerWarp; c += 32) finish_row32(p, &sum[c], m, row_off, (int64_t)n_t * BN + col0 + c);
+    }
+  } else {
+    // ------------------------------- split warps: A -> hi / lo halves in TMEM -------------------------------
+    const int quarter = warp & 3;
+    const int colhalf = (warp - C::kSplitWarp0) >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kASplitCol0 + colhalf * 16;
+    const uint32_t split_pair0 = map_to_cta(bar_split, 0);
+    int s = 0, slot = 0;
+    uint32_t ph = 0;
+    // The slot was last read by the MMAs of the k-block kSlots before this one; they release shared-memory
+    // stage `rs` (the stage that k-block used) through empty[rs], whose phase `rph` this thread tracks.
+    int rs = 0;
+    uint32_t rph = 0;
+    int64_t n = 0;  // k-blocks processed so far by this CTA
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int kb = 0; kb < p.num_kb; ++kb, ++n) {
+        if (n >= C::kSlots) {
+          if (!(ok = mbar_wait(bar_empty + 8 * rs, rph, abort_flag, p.status, 32u))) break;
+          if (++rs == kStages) { rs = 0; rph ^= 1; }
+        }
+        if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 16u))) break;
+        const float4 *arow = reinterpret_cast<const float4 *>(smem + (size_t)s * C::kStageBytes + row * 128);
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float4 x = arow[(colhalf * 4 + c) ^ (row & 7)];
+          const float h0 = to_tf32_rna(x.x), h1 = to_tf32_rna(x.y), h2 = to_tf32_rna(x.z), h3 = to_tf32_rna(x.w);
+          hi[4 * c + 0] = __float_as_uint(h0); hi[4 * c + 1] = __float_as_uint(h1);
+          hi[4 * c + 2] = __float_as_uint(h2); hi[4 * c + 3] = __float_as_uint(h3);
+          lo[4 * c + 0] = __float_as_uint(to_tf32_rna(x.x - h0)); lo[4 * c + 1] = __float_as_uint(to_tf32_rna(x.y - h1));
+          lo[4 * c + 2] = __float_as_uint(to_tf32_rna(x.z - h2)); lo[4 * c + 3] = __float_as_uint(to_tf32_rna(x.w - h3));
+        }
+        tc_fence_after();
+        tmem_st16(a_lane + (uint32_t)slot * 64, hi);
+        tmem_st16(a_lane + (uint32_t)slot * 64 + 32, lo);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          // the even CTA's own barrier takes a plain arrival; the partner's crosses the cluster without a release
+          if (rank == 0) mbar_arrive(bar_split + 8 * slot);
+          else mbar_arrive_cluster_relaxed(split_pair0 + 8 * slot);
+        }
+        if (++s == kStages) { s = 0; ph ^= 1; }
+        if (++slot == C::kSlots) slot = 0;
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (s_abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::kTmemCols);
+  }
+}
+
+// hi = tf32(x), lo = tf32(x - hi) of a [rows, cols] matrix with row pitch ld, written densely (pitch ldp)
+__global__ void __launch_bounds__(256)
+split_tf32_kernel(const float *__restrict__ x, float *__restrict__ hi, float *__restrict__ lo, int64_t rows, int64_t cols4,
+                  int64_t ld, int64_t ldp) {
+  const int64_t total = rows * cols4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols4, c = (i - r * cols4) * 4;
+    const float4 v = *reinterpret_cast<const float4 *>(x + r * ld + c);
+    float4 h, l;
+    h.x = to_tf32_rna(v.x); h.y = to_tf32_rna(v.y); h.z = to_tf32_rna(v.z); h.w = to_tf32_rna(v.w);
+    l.x = to_tf32_rna(v.x - h.x); l.y = to_tf32_rna(v.y - h.y); l.z = to_tf32_rna(v.z - h.z); l.w = to_tf32_rna(v.w - h.w);
+    *reinterpret_cast<float4 *>(hi + r * ldp + c) = h;
+    *reinterpret_cast<float4 *>(lo + r * ldp + c) = l;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side: tensor-map encoding and launch
 // ---------------------------------------------------------------------------------------------
@@ -801,6 +1074,38 @@ int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, G
   const int64_t pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
   kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_tc_pair");
+}
+
+template <bool B_MN>
+int launch_pair3(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mbh, const CUtensorMap &mbl, GemmParams &p) {
+  using C = Cfg3P;
+  auto kern = gemm_tc_pair3_kernel<B_MN>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+    return fail(B200_ECUDA, "gemm(tc pair3): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  static int max_pairs[64] = {};  // per device, as in launch_pair
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ECUDA, "gemm(tc pair3): bad device");
+  if (max_pairs[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kNumSMs, 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1)
+      return fail(B200_ECUDA, "gemm(tc pair3): cudaOccupancyMaxActiveClusters failed");
+    max_pairs[dev] = n;
+  }
+  const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
+  const int64_t pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+  kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mbh, mbl, p);
+  return check_launch("gemm_tc_pair3");
 }
 
 template <bool B_MN, bool SPLIT3>
@@ -910,14 +1215,30 @@ bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, 
   return true;
 }
 
+// 3xTF32 with a workspace: B is split once into dense hi / lo copies (row pitch = columns rounded up to 4)
+// and the CTA-pair kernel runs. Qualifies: one matrix (no batch), more than one row tile, B rows a multiple of
+// four floats long.
+static bool pair3_qualifies(const b200_gemm_desc &d) {
+  const int64_t cols = d.trans_b ? d.K : d.N;
+  return d.math_mode == B200_MATH_FP32X3 && d.batch_outer * d.batch_inner == 1 && d.M > BM && cols % 4 == 0;
+}
+
+size_t gemm_tc_workspace_bytes(const b200_gemm_desc &d) {
+  if (!pair3_qualifies(d)) return 0;
+  const int64_t rows = d.trans_b ? d.N : d.K, cols = d.trans_b ? d.K : d.N;
+  return 2 * align256((size_t)rows * (size_t)cols * 4);
+}
+
 int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
-            const float *residual, float *Y) {
+            const float *residual, float *Y, void *workspace, size_t workspace_bytes) {
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
-  const int bn = pick_bn(d.N, split3);
+  const bool pair3 = workspace && aligned16(workspace) && pair3_qualifies(d) &&
+                     workspace_bytes >= gemm_tc_workspace_bytes(d);
+  const int bn = pair3 ? 128 : pick_bn(d.N, split3);
   // CTA pairs (256 x 256 tiles) for TF32 GEMMs with wide N and at least two row tiles per matrix
   const bool pair = !split3 && bn == 256 && d.M > BM;
 
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mb_lo;
   GemmParams p{};
   {
     uint64_t dims[4] = {(uint64_t)d.K, (uint64_t)d.M, 1, 1};
@@ -940,9 +1261,26 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
     str[0] = (uint64_t)d.ldb * 4;
     batch_axis(d.batch_inner, d.b_stride_inner, fb, &dims[2], &str[1], &p.b_bi);
     batch_axis(d.batch_outer, d.b_stride_outer, fb, &dims[3], &str[2], &p.b_bo);
-    if (int rc = encode_map(&mb, B, dims, str, d.trans_b ? BK : 32, d.trans_b ? (uint32_t)(pair ? bn / 2 : bn) : BK,
-                            d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+    if (pair3) {
+      // split B into the workspace, then describe the two dense copies instead of B itself
+      const int64_t rows = d.trans_b ? d.N : d.K, cols = d.trans_b ? d.K : d.N;
+      float *b_hi = static_cast<float *>(workspace);
+      float *b_lo = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)rows * cols * 4));
+      const int64_t total4 = rows * (cols / 4);
+      int64_t grid = (total4 + 255) / 256;
+      if (grid > (int64_t)kNumSMs * 8) grid = (int64_t)kNumSMs * 8;
+      split_tf32_kernel<<<(unsigned)grid, 256, 0, st>>>(B, b_hi, b_lo, rows, cols / 4, d.ldb, cols);
+      if (int rc = check_launch("split_tf32")) return rc;
+      str[0] = (uint64_t)cols * 4;
+      const uint32_t box0 = d.trans_b ? BK : 32, box1 = d.trans_b ? (uint32_t)(bn / 2) : BK;
+      const CUtensorMapSwizzle sw = d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+      if (int rc = encode_map(&mb, b_hi, dims, str, box0, box1, sw)) return rc;
+      if (int rc = encode_map(&mb_lo, b_lo, dims, str, box0, box1, sw)) return rc;
+    } else if (int rc = encode_map(&mb, B, dims, str, d.trans_b ? BK : 32,
+                                   d.trans_b ? (uint32_t)(pair ? bn / 2 : bn) : BK,
+                                   d.trans_b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) {
       return rc;
+    }
   }
   // Widest access that every output (and residual) row segment is aligned for.
   auto aligned_to = [&](int elems) {
@@ -969,6 +1307,11 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   p.status = device_status_ptr();
   if (!p.status) return fail(B200_ECUDA, "gemm(tc): device status word unavailable");
 
+  if (pair3) {
+    p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));  // 256-row tile pairs
+    p.num_tiles_batch = 1;
+    return d.trans_b ? launch_pair3<false>(st, ma, mb, mb_lo, p) : launch_pair3<true>(st, ma, mb, mb_lo, p);
+  }
   if (pair) {
     p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));  // 256-row tile pairs
     p.num_tiles_batch = d.batch_outer * d.batch_inner;

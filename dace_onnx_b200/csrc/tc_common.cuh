@@ -201,6 +201,12 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster_addr
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
+// The same arrival without release semantics. A cluster-scope release makes the arriving thread wait until its
+// earlier writes are visible cluster-wide (measured: ~1400 clk per arrival); callers whose only earlier work is
+// tcgen05 traffic, already ordered by tcgen05.wait + tcgen05.fence::before_thread_sync, do not need it.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
 // TMA load into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair
 __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
                                                  int c0, int c1, int c2, int c3) {
@@ -227,6 +233,16 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc,
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// the same with the A operand read from TMEM (each CTA's 128 rows at the same TMEM address in both CTAs)
+__device__ __forceinline__ void umma_tf32_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                  uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // one arrival on the barrier at `bar_cluster_addr` (either CTA) when all MMAs issued so far are done

@@ -54,9 +54,28 @@ def gemm_raw(A, B, Y, *, batch_outer=1, batch_inner=1, M, N, K, lda, ldb, ldy, a
     """Direct call of b200_gemm_f32 with explicit strides (A, B, Y are base tensors of the views)."""
     d = GemmDesc(batch_outer, batch_inner, M, N, K, lda, ldb, ldy, a_strides[0], a_strides[1], b_strides[0],
                  b_strides[1], y_strides[0], y_strides[1], int(trans_b), epilogue, float(scale), _math(math_mode))
-    check(_lib.load().b200_gemm_f32(_stream(), ctypes.byref(d), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual),
-                                    _ptr(Y)))
+    lib = _lib.load()
+    need = lib.b200_gemm_workspace_bytes(ctypes.byref(d))
+    if need:
+        ws = _gemm_workspace(Y.device, need)
+        check(lib.b200_gemm_ws_f32(_stream(), ctypes.byref(d), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual), _ptr(Y),
+                                   _ptr(ws), ws.numel()))
+    else:
+        check(lib.b200_gemm_f32(_stream(), ctypes.byref(d), _ptr(A), _ptr(B), _ptr(bias), _ptr(residual), _ptr(Y)))
     return Y
+
+
+_GEMM_WS = {}
+
+
+def _gemm_workspace(device, nbytes):
+    """Scratch for b200_gemm_ws_f32, one buffer per (device, stream), grown on demand: calls on one stream are
+    ordered, so they can share it; calls on different streams must not."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _GEMM_WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = _GEMM_WS[key] = torch.empty(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
+    return ws
 
 
 def _batch_view(shape, mat_elems):

@@ -100,6 +100,17 @@ typedef struct b200_gemm_desc {
 B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
                   const float *bias, const float *residual, float *Y);
 
+/* The same contraction with device scratch, the way the reference's library-call expansions get a workspace
+ * from their SDFG init hook (cudnn_implementations.py:281-301). With b200_gemm_workspace_bytes(desc) bytes of
+ * 16-byte aligned scratch (0 = this call has no use for one), the fp32-accurate mode (B200_MATH_FP32X3) splits
+ * B once into its two TF32 halves there and runs a faster two-CTA kernel; results follow the same 3xTF32
+ * arithmetic as b200_gemm_f32. A null or too small workspace is not an error: the call then behaves exactly
+ * like b200_gemm_f32. The scratch is only used during the call (stream-ordered). */
+B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_desc *desc);
+B200_API int b200_gemm_ws_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
+                              const float *bias, const float *residual, float *Y, void *workspace,
+                              size_t workspace_bytes);
+
 /* Fused attention: out = Softmax(Q K^T * scale, axis=-1) V per (batch, head), the node pattern
  * MatMul -> Mul(constant) -> Softmax -> MatMul of the exported BERT graph (each node as in
  * pure_implementations.py:130-235, :87-89, :346-366) without writing the [seq, seq] scores to memory.
