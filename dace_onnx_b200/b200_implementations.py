@@ -91,10 +91,9 @@ def _two_level_batch(batch_shape, sa, sb, sy):
 # ---------------------------------------------------------------------------------------------
 # C++ tasklet bodies (pure string builders)
 # ---------------------------------------------------------------------------------------------
-def tasklet_matmul(a_shape, b_shape, label="MatMul", trans_b=False, bias=False, mode=None):
-    """Body for MatMul (A,B -> Y) or Gemm with transB=1 (A,B[,C] -> Y). Returns C++ or None when the
-    broadcast batch cannot be expressed with two strided levels."""
-    mode = math_mode() if mode is None else mode
+def _gemm_desc_init(a_shape, b_shape, trans_b, bias, mode):
+    """Initializer list of the b200_gemm_desc of a MatMul / Gemm node, or None when the broadcast batch cannot
+    be expressed with two strided levels."""
     M, K = int(a_shape[-2]), int(a_shape[-1])
     N = int(b_shape[-2]) if trans_b else int(b_shape[-1])
     batch, _, _ = _broadcast(a_shape[:-2], b_shape[:-2])
@@ -108,14 +107,45 @@ def tasklet_matmul(a_shape, b_shape, label="MatMul", trans_b=False, bias=False, 
     if levels is None:
         return None
     (bo, ao, bbo, yo), (bi, ai, bbi, yi) = levels
-    ldb = int(b_shape[-1])
-    epi = 1 if bias else 0
-    return """
-    b200_gemm_desc __b200_d = {{{bo}, {bi}, {M}, {N}, {K}, {K}, {ldb}, {N}, {ao}, {ai}, {bbo}, {bbi}, {yo}, {yi},
-                               {tb}, {epi}, 1.0f, {mode}}};
-    int __b200_rc = b200_gemm_f32(__dace_current_stream, &__b200_d, _A, _B, {bias}, nullptr, _Y);
-""".format(bo=bo, bi=bi, M=M, N=N, K=K, ldb=ldb, ao=ao, ai=ai, bbo=bbo, bbi=bbi, yo=yo, yi=yi, tb=int(trans_b),
-           epi=epi, mode=mode, bias="_C" if bias else "nullptr") + CHECK.format(label=label)
+    return "{{{bo}, {bi}, {M}, {N}, {K}, {K}, {ldb}, {N}, {ao}, {ai}, {bbo}, {bbi}, {yo}, {yi}, {tb}, {epi}, 1.0f, {mode}}}".format(
+        bo=bo, bi=bi, M=M, N=N, K=K, ldb=int(b_shape[-1]), ao=ao, ai=ai, bbo=bbo, bbi=bbi, yo=yo, yi=yi,
+        tb=int(trans_b), epi=1 if bias else 0, mode=mode)
+
+
+def tasklet_matmul(a_shape, b_shape, label="MatMul", trans_b=False, bias=False, mode=None, ws=None):
+    """Body for MatMul (A,B -> Y) or Gemm with transB=1 (A,B[,C] -> Y). Returns C++ or None when the
+    broadcast batch cannot be expressed with two strided levels. With `ws` (the name of a workspace in the SDFG
+    state, see gemm_env_code) the call goes through b200_gemm_ws_f32."""
+    mode = math_mode() if mode is None else mode
+    init = _gemm_desc_init(a_shape, b_shape, trans_b, bias, mode)
+    if init is None:
+        return None
+    if ws is None:
+        call = "b200_gemm_f32(__dace_current_stream, &__b200_d, _A, _B, {bias}, nullptr, _Y)"
+    else:
+        call = ("b200_gemm_ws_f32(__dace_current_stream, &__b200_d, _A, _B, {bias}, nullptr, _Y,\n"
+                "                                     __state->{ws}, __state->{ws}_bytes)")
+    return ("\n    b200_gemm_desc __b200_d = " + init + ";\n    int __b200_rc = " +
+            call.format(bias="_C" if bias else "nullptr", ws=ws) + ";\n") + CHECK.format(label=label)
+
+
+def gemm_env_code(a_shape, b_shape, ws_name, trans_b=False, bias=False, mode=None):
+    """(state_fields, init_code, finalize_code) of a MatMul / Gemm node whose call can use device scratch
+    (b200_gemm_workspace_bytes > 0 for its descriptor): allocated once at SDFG initialisation, freed at exit,
+    as cudnn_implementations.py:281-301 does for cuDNN's workspace."""
+    mode = math_mode() if mode is None else mode
+    init_list = _gemm_desc_init(a_shape, b_shape, trans_b, bias, mode)
+    fields = ["void *%s;" % ws_name, "size_t %s_bytes;" % ws_name]
+    init = """
+    {{
+        b200_gemm_desc d = {init};
+        __state->{ws}_bytes = b200_gemm_workspace_bytes(&d);
+        __state->{ws} = nullptr;
+        if (__state->{ws}_bytes) cudaMalloc(&__state->{ws}, __state->{ws}_bytes);
+    }}
+""".format(init=init_list, ws=ws_name)
+    fini = "\n    if (__state->{ws}) cudaFree(__state->{ws});\n".format(ws=ws_name)
+    return fields, init, fini
 
 
 def tasklet_conv(x_shape, w_shape, pads, strides, bias, label="Conv", mode=None):
@@ -279,14 +309,29 @@ def _register():
         Impl.__doc__ = "b200 expansion of ONNX%s through libb200ops." % op
         _REGISTERED[op] = op_implementation(op=op, name="b200")(Impl)
 
+    def gemm_build(node, d, trans_b, bias):
+        # fp32-accurate mode: the node gets device scratch from the SDFG state, like the cuDNN expansion
+        if math_mode() != 0:
+            return tasklet_matmul(d["A"].shape, d["B"].shape, node.label, trans_b=trans_b, bias=bias), None
+        ws = "b200_ws_%s" % "".join(ch if ch.isalnum() else "_" for ch in node.label)
+        fields, init, fini = gemm_env_code(d["A"].shape, d["B"].shape, ws, trans_b=trans_b, bias=bias)
+
+        class GemmEnv(B200Ops):
+            state_fields = fields
+            init_code = init
+            finalize_code = fini
+        GemmEnv.__name__ = ws + "_environment"
+        env = dace.library.environment(GemmEnv)
+        return tasklet_matmul(d["A"].shape, d["B"].shape, node.label, trans_b=trans_b, bias=bias, ws=ws), env
+
     make("MatMul", ["A", "B"], ["Y"],
          lambda node, d: len(d["A"].shape) > 1 and len(d["B"].shape) > 1 and
          tasklet_matmul(d["A"].shape, d["B"].shape) is not None,
-         lambda node, d: (tasklet_matmul(d["A"].shape, d["B"].shape, node.label), None))
+         lambda node, d: gemm_build(node, d, False, False))
     make("Gemm", ["A", "B", "C"], ["Y"],
          lambda node, d: node.alpha == 1.0 and node.beta == 1.0 and node.transA == 0 and node.transB == 1 and
          ("C" not in d or _prod(d["C"].shape) == d["B"].shape[0]),
-         lambda node, d: (tasklet_matmul(d["A"].shape, d["B"].shape, node.label, trans_b=True, bias="C" in d), None))
+         lambda node, d: gemm_build(node, d, True, "C" in d))
 
     def conv_build(node, d):
         pads = node.pads if node.pads is not None else [0, 0, 0, 0]

@@ -754,26 +754,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //   split[s]   even CTA: one arrival per split warp of both CTAs (A halves of stage s are in TMEM)
 //   tfull[a]   own CTA: multicast commit                    tempty[a] even CTA: one arrival per epilogue warp of both
 // ---------------------------------------------------------------------------------------------
+// BN_ = 128 or 192 tile columns. One thread issues every MMA at ~68 clk per instruction, which for N = 128
+// (64 clk of tensor work on the pair) leaves the tensor cores waiting; N = 192 instructions (96 clk) hide it.
+template <int BN_>
 struct Cfg3P {
-  static constexpr int BN = 128;
-  static constexpr int kBHalfBytes = (BN / 2) * BK * 4;                  // 8 KiB: 64 tile columns of one B half
+  static constexpr int BN = BN_;
+  static constexpr int kBHalfBytes = (BN / 2) * BK * 4;                  // half the tile columns of one B half
   static constexpr int kStageBytes = A_STAGE_BYTES + 2 * kBHalfBytes;    // A raw | B_hi | B_lo
-  static constexpr int kStages = 6;                                      // shared-memory ring (TMA runs this far ahead)
-  static constexpr int kSlots = 4;                                       // A hi/lo slots in TMEM (64 columns each)
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 6 ? 6 : (200 * 1024) / kStageBytes;  // TMA run-ahead
+  static constexpr int kSlots = (512 - 2 * BN) / 64;                     // A hi/lo slots in TMEM (64 columns each)
   static constexpr int kASplitCol0 = 2 * BN;
   static constexpr int kTmemCols = 512;
-  static constexpr int kEpilogueWarps = 8, kSplitWarps = 8;
+  static constexpr int kColsPerWarp = 64;
+  static constexpr int kEpilogueWarps = 4 * (BN / kColsPerWarp), kSplitWarps = 8;
   static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kSplitWarps);
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-  static constexpr int kColsPerWarp = BN / 2;
 };
 
-template <bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg3P::kThreads, 1)
+template <int BN_, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg3P<BN_>::kThreads, 1)
 gemm_tc_pair3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_bh,
                      const __grid_constant__ CUtensorMap map_bl, const GemmParams p) {
-  using C = Cfg3P;
+  using C = Cfg3P<BN_>;
   constexpr int kStages = C::kStages;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
@@ -1076,10 +1079,10 @@ int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, G
   return check_launch("gemm_tc_pair");
 }
 
-template <bool B_MN>
+template <int BN, bool B_MN>
 int launch_pair3(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mbh, const CUtensorMap &mbl, GemmParams &p) {
-  using C = Cfg3P;
-  auto kern = gemm_tc_pair3_kernel<B_MN>;
+  using C = Cfg3P<BN>;
+  auto kern = gemm_tc_pair3_kernel<BN, B_MN>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
     return fail(B200_ECUDA, "gemm(tc pair3): cannot set dynamic shared memory to %d", C::kSmemBytes);
   static int max_pairs[64] = {};  // per device, as in launch_pair
@@ -1234,7 +1237,9 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   const bool pair3 = workspace && aligned16(workspace) && pair3_qualifies(d) &&
                      workspace_bytes >= gemm_tc_workspace_bytes(d);
-  const int bn = pair3 ? 128 : pick_bn(d.N, split3);
+  // pair kernel: 192-column tiles unless their padding costs more than the slower 128-column instructions
+  const bool pair3_wide = ((d.N + 191) / 192) * 192 <= ((d.N + 127) / 128) * 128 * 1.3;
+  const int bn = pair3 ? (pair3_wide ? 192 : 128) : pick_bn(d.N, split3);
   // CTA pairs (256 x 256 tiles) for TF32 GEMMs with wide N and at least two row tiles per matrix
   const bool pair = !split3 && bn == 256 && d.M > BM;
 
@@ -1310,7 +1315,9 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const floa
   if (pair3) {
     p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));  // 256-row tile pairs
     p.num_tiles_batch = 1;
-    return d.trans_b ? launch_pair3<false>(st, ma, mb, mb_lo, p) : launch_pair3<true>(st, ma, mb, mb_lo, p);
+    if (bn == 192)
+      return d.trans_b ? launch_pair3<192, false>(st, ma, mb, mb_lo, p) : launch_pair3<192, true>(st, ma, mb, mb_lo, p);
+    return d.trans_b ? launch_pair3<128, false>(st, ma, mb, mb_lo, p) : launch_pair3<128, true>(st, ma, mb, mb_lo, p);
   }
   if (pair) {
     p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));  // 256-row tile pairs

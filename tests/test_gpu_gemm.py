@@ -121,3 +121,55 @@ def test_bad_arguments_raise(cuda):
     with pytest.raises(NotImplementedError):
         ops.gemm(a, a, transB=0)
     assert ops.matmul(torch.zeros(0, 8, device="cuda"), torch.zeros(8, 3, device="cuda")).shape == (0, 3)
+
+
+# ---- the workspace entry point: 3xTF32 with B split once per call, CTA-pair kernel ----------------------------
+def _gemm_call(ws_bytes, M, N, K, trans_b, epi, A, B, bias, res, mode=0):
+    import ctypes
+    from dace_onnx_b200 import _lib
+    lib = _lib.load()
+    Y = torch.empty(M, N, device="cuda")
+    d = _lib.GemmDesc(1, 1, M, N, K, K, K if trans_b else N, N, 0, 0, 0, 0, 0, 0, int(trans_b), epi, 0.5, mode)
+    need = lib.b200_gemm_workspace_bytes(ctypes.byref(d))
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if ws_bytes is None:
+        _lib.check(lib.b200_gemm_f32(st, ctypes.byref(d), p(A), p(B), p(bias), p(res), p(Y)))
+    else:
+        n = need if ws_bytes == "need" else ws_bytes
+        ws = torch.empty(max(n, 16), device="cuda", dtype=torch.uint8)
+        _lib.check(lib.b200_gemm_ws_f32(st, ctypes.byref(d), p(A), p(B), p(bias), p(res), p(Y), p(ws) if n else None, n))
+    return Y, need
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+@pytest.mark.parametrize("M,N,K", [(256, 192, 32), (384, 128, 96), (1000, 260, 136), (129, 64, 32), (4096, 768, 768),
+                                    (2048, 3072, 768), (513, 1024, 100), (300, 8, 40)])
+def test_gemm_workspace_path(M, N, K, trans_b, cuda):
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    A = torch.randn(M, K, generator=g)
+    B = torch.randn((N, K) if trans_b else (K, N), generator=g) * 0.1
+    bias, res = torch.randn(N, generator=g), torch.randn(M, N, generator=g)
+    ref = po.MatMul(A, B.t().contiguous() if trans_b else B)
+    for epi, want in ((0, ref), (EPI_BIAS, po.Add(ref, bias)), (EPI_BIAS_RESIDUAL, po.Add(po.Add(ref, bias), res)),
+                      (EPI_BIAS_GELU, po.GeluChain(po.Add(ref, bias))), (EPI_SCALE, po.Mul(ref, np.float32(0.5)))):
+        Y, need = _gemm_call("need", M, N, K, trans_b, epi, A.cuda(), B.cuda(), bias.cuda(), res.cuda())
+        assert need == 2 * ((N * K * 4 + 255) // 256 * 256)
+        close(Y, want, RTOL, ATOL)
+
+
+def test_gemm_workspace_is_optional(cuda):
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 640, 384, 256
+    A, B, bias = torch.randn(M, K, generator=g).cuda(), torch.randn(N, K, generator=g).cuda(), torch.randn(N, generator=g).cuda()
+    plain, need = _gemm_call(None, M, N, K, True, EPI_BIAS, A, B, bias, None)
+    assert need > 0
+    for ws in (0, need - 256):                      # absent or too small: exactly the plain entry point's result
+        y, _ = _gemm_call(ws, M, N, K, True, EPI_BIAS, A, B, bias, None)
+        assert torch.equal(y, plain)
+    y, _ = _gemm_call("need", M, N, K, True, EPI_BIAS, A, B, bias, None)
+    close(y, plain, RTOL, ATOL)                     # same 3xTF32 arithmetic, different accumulation grouping
+    # no scratch is asked for where the pair kernel does not apply: other modes, single row tile, ragged B rows
+    assert _gemm_call(None, M, N, K, True, EPI_BIAS, A, B, bias, None, mode=1)[1] == 0
+    assert _gemm_call(None, 128, N, K, True, EPI_BIAS, A[:128].contiguous(), B, bias, None)[1] == 0
+    assert _gemm_call(None, M, N, 254, True, EPI_BIAS, A[:, :254].contiguous(), B[:, :254].contiguous(), bias, None)[1] == 0

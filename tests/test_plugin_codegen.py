@@ -32,6 +32,8 @@ def bodies():
         impl.tasklet_matmul((64, 512, 768), (768, 768), mode=0),
         impl.tasklet_matmul((64, 12, 512, 64), (64, 12, 64, 512), mode=1),
         impl.tasklet_matmul((4096, 784), (120, 784), trans_b=True, bias=True, mode=2),
+        impl.tasklet_matmul((64, 512, 768), (768, 768), mode=0, ws="ws"),
+        impl.tasklet_matmul((4096, 784), (120, 784), trans_b=True, bias=True, mode=0, ws="ws"),
         impl.tasklet_conv((256, 64, 56, 56), (64, 64, 3, 3), (1, 1, 1, 1), (1, 1), True, mode=0).replace("{ws}", "ws"),
         impl.tasklet_softmax((768, 512, 512), -1),
         impl.tasklet_softmax((2, 4, 10), 0, log=True),
@@ -46,8 +48,32 @@ def bodies():
     return out
 
 
+def hooks():
+    """init / finalize code of the nodes that keep a workspace in the SDFG state."""
+    out = []
+    for fields, init, fini in (
+            impl.gemm_env_code((64, 512, 768), (768, 768), "ws", mode=0),
+            impl.gemm_env_code((4096, 784), (120, 784), "ws", trans_b=True, bias=True, mode=0),
+            impl.conv_env_code((256, 64, 56, 56), (64, 64, 3, 3), (1, 1, 1, 1), (1, 1), "ws", mode=0)):
+        assert fields == ["void *ws;", "size_t ws_bytes;"]
+        out += [init, fini]
+    return out
+
+
+HOOK_HEAD = """
+extern "C" int cudaMalloc(void **, size_t);
+extern "C" int cudaFree(void *);
+"""
+HOOK_WRAP = """
+void hook_{i}(State *__state) {{
+{body}
+}}
+"""
+
+
 def test_tasklets_compile_against_the_header():
-    src = HEAD + "\n".join(WRAP.format(i=i, body=b) for i, b in enumerate(bodies()))
+    src = HEAD + "\n".join(WRAP.format(i=i, body=b) for i, b in enumerate(bodies())) + HOOK_HEAD + \
+        "\n".join(HOOK_WRAP.format(i=i, body=b) for i, b in enumerate(hooks()))
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "tasklets.cpp")
         with open(path, "w") as f:
@@ -65,6 +91,8 @@ def test_matmul_descriptor_fields():
     assert "{1, 64, 512, 768, 768, 768, 768, 768, 0, 393216, 0, 0, 0, 393216," in code.replace("\n", " ").replace("  ", " ")
     assert impl.tasklet_matmul((2, 3, 4, 5, 6), (3, 1, 6, 7), mode=0) is None or "b200_gemm_f32" in \
         impl.tasklet_matmul((2, 3, 4, 5, 6), (3, 1, 6, 7), mode=0)
+    with_ws = impl.tasklet_matmul((64, 512, 768), (768, 768), mode=0, ws="b200_ws_n1")
+    assert "b200_gemm_ws_f32(" in with_ws and "__state->b200_ws_n1_bytes" in with_ws
 
 
 def test_broadcast_strides():
