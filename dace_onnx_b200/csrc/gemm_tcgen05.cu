@@ -78,8 +78,11 @@ __device__ __forceinline__ void st_global_v8(float *p, const float *v) {
 // Fused epilogue and store of 32 consecutive columns [n0, n0+32) of output row m, held in registers
 // by one thread. Each thread owns 128 contiguous bytes of its row; with 32-byte vector accesses every
 // store instruction writes whole 32-byte sectors (vec == 8), else 16-byte or scalar accesses.
+// `bias_s`: when not null, the 32 bias values of these columns staged in shared memory (zero past N), read as
+// broadcast 128-bit loads instead of global loads whose latency would serialise the store phase.
 template <int EPI>
-__device__ __forceinline__ void finish_row32_t(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0) {
+__device__ __forceinline__ void finish_row32_t(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0,
+                                               const float *bias_s = nullptr) {
   constexpr bool kBias = EPI == B200_EPI_BIAS || EPI == B200_EPI_BIAS_RELU || EPI == B200_EPI_BIAS_GELU ||
                          EPI == B200_EPI_BIAS_RESIDUAL;
   constexpr bool kResidual = EPI == B200_EPI_BIAS_RESIDUAL;
@@ -93,7 +96,11 @@ __device__ __forceinline__ void finish_row32_t(const GemmParams &p, float *v, in
 #pragma unroll
     for (int i = 0; i < 8; ++i) b[i] = r[i] = 0.f;
     if (kBias) {
-      if (full) {
+      if (bias_s) {
+        const float4 b0 = *reinterpret_cast<const float4 *>(bias_s + j);
+        const float4 b1 = *reinterpret_cast<const float4 *>(bias_s + j + 4);
+        b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+      } else if (full) {
         const float4 b0 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j));
         const float4 b1 = __ldg(reinterpret_cast<const float4 *>(p.bias + n0 + j + 4));
         b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
@@ -133,12 +140,13 @@ __device__ __forceinline__ void finish_row32_t(const GemmParams &p, float *v, in
 }
 
 // The epilogue kind is uniform for the launch: choose the specialised body once per 32x32 block.
-__device__ __forceinline__ void finish_row32(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0) {
+__device__ __forceinline__ void finish_row32(const GemmParams &p, float *v, int64_t m, int64_t row_off, int64_t n0,
+                                             const float *bias_s = nullptr) {
   switch (p.epilogue) {
-    case B200_EPI_BIAS: finish_row32_t<B200_EPI_BIAS>(p, v, m, row_off, n0); break;
-    case B200_EPI_BIAS_RELU: finish_row32_t<B200_EPI_BIAS_RELU>(p, v, m, row_off, n0); break;
-    case B200_EPI_BIAS_GELU: finish_row32_t<B200_EPI_BIAS_GELU>(p, v, m, row_off, n0); break;
-    case B200_EPI_BIAS_RESIDUAL: finish_row32_t<B200_EPI_BIAS_RESIDUAL>(p, v, m, row_off, n0); break;
+    case B200_EPI_BIAS: finish_row32_t<B200_EPI_BIAS>(p, v, m, row_off, n0, bias_s); break;
+    case B200_EPI_BIAS_RELU: finish_row32_t<B200_EPI_BIAS_RELU>(p, v, m, row_off, n0, bias_s); break;
+    case B200_EPI_BIAS_GELU: finish_row32_t<B200_EPI_BIAS_GELU>(p, v, m, row_off, n0, bias_s); break;
+    case B200_EPI_BIAS_RESIDUAL: finish_row32_t<B200_EPI_BIAS_RESIDUAL>(p, v, m, row_off, n0, bias_s); break;
     case B200_EPI_SCALE: finish_row32_t<B200_EPI_SCALE>(p, v, m, row_off, n0); break;
     default: finish_row32_t<B200_EPI_NONE>(p, v, m, row_off, n0); break;
   }
@@ -769,7 +777,7 @@ struct Cfg3P {
   static constexpr int kEpilogueWarps = 4 * (BN / kColsPerWarp), kSplitWarps = 8;
   static constexpr int kSplitWarp0 = 2 + kEpilogueWarps;
   static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kSplitWarps);
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kEpilogueWarps * kColsPerWarp * 4;  // + barriers + staged bias
 };
 
 template <int BN_, bool B_MN>
@@ -787,6 +795,7 @@ gemm_tc_pair3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t bar_split = bar_empty + 8 * kStages;  // one per TMEM slot
   const uint32_t bar_tfull = bar_split + 8 * C::kSlots;
   const uint32_t bar_tempty = bar_tfull + 16;
+  float *bias_all = reinterpret_cast<float *>(smem + kStages * C::kStageBytes + 256);  // 64 bias values per epilogue warp
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -910,6 +919,15 @@ gemm_tc_pair3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const int64_t m = (int64_t)(2 * m_t + (int)rank) * BM + quarter * 32 + lane;
       const int64_t row_off = m * p.ldy;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      // Stage this warp's 64 bias values in its own shared-memory slice while the tile's first chunk is
+      // still being computed: the store phase then reads them as broadcast 128-bit loads.
+      float *bias_s = bias_all + ew * C::kColsPerWarp;
+      if (p.bias) {
+        const int64_t n = (int64_t)n_t * BN + col0 + lane;
+        bias_s[lane] = n < p.N ? __ldg(p.bias + n) : 0.f;
+        bias_s[32 + lane] = n + 32 < p.N ? __ldg(p.bias + n + 32) : 0.f;
+      }
+      __syncwarp();
       float sum[C::kColsPerWarp];
 #pragma unroll
       for (int j = 0; j < C::kColsPerWarp; ++j) sum[j] = 0.f;
@@ -934,7 +952,9 @@ gemm_tc_pair3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       }
       if (!ok) break;
 #pragma unroll
-      for (int c = 0; c < C::kColsPerWarp; c += 32) finish_row32(p, &sum[c], m, row_off, (int64_t)n_t * BN + col0 + c);
+      for (int c = 0; c < C::kColsPerWarp; c += 32)
+        finish_row32(p, &sum[c], m, row_off, (int64_t)n_t * BN + col0 + c, p.bias ? bias_s + c : nullptr);
+      __syncwarp();  // all lanes have read the staged bias before the next tile's values replace it
     }
   } else {
     // ------------------------------- split warps: A -> hi / lo halves in TMEM -------------------------------
