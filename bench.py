@@ -308,6 +308,21 @@ def kernel_cases(device):
                 2 * m * n * k, 4 * (m * k + n * k + m * n), "tensor"
         return make
 
+    def gemm_no_workspace(m, n, k, mode, epi=EPI_BIAS):
+        # the plain entry point (b200_gemm_f32): in 3xTF32 mode the single-CTA kernel that splits B in shared memory
+        def make():
+            import ctypes
+            from dace_onnx_b200 import _lib
+            a, w, b = rn(m, k), rn(n, k, std=0.02), rn(n, std=0.02)
+            y = torch.empty(m, n, device=device)
+            d = _lib.GemmDesc(1, 1, m, n, k, k, k, n, 0, 0, 0, 0, 0, 0, 1, epi, 1.0, _lib.MATH_MODES[mode])
+            lib = _lib.load()
+            ptr = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+            fn = lambda: _lib.check(lib.b200_gemm_f32(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),  # noqa
+                                                      ctypes.byref(d), ptr(a), ptr(w), ptr(b), None, ptr(y)))
+            return fn, 2 * m * n * k, 4 * (m * k + n * k + m * n), "tensor"
+        return make
+
     def attn_qk(b, h, s, d, mode):
         def make():
             qkv = rn(b, s, 3 * h * d)
@@ -417,6 +432,7 @@ def kernel_cases(device):
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),
         "gemm_tf32_ffn2": gemm(16384, 1024, 4096, "tf32"), "gemm_tf32_proj": gemm(16384, 1024, 1024, "tf32"),
         "gemm_fp32x3_ffn1": gemm(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU), "gemm_fp32x3_proj": gemm(16384, 768, 768, "fp32x3"),
+        "gemm_fp32x3_ffn1_no_workspace": gemm_no_workspace(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
         "attention_fused_tf32": attn_fused(32, 16, 384, 64),
         "attention_fused_tf32_headmajor": attn_fused_headmajor(32, 16, 384, 64),
