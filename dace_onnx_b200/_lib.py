@@ -70,6 +70,7 @@ SIGNATURES = {
                                 POINTER(c_int64), POINTER(c_int64)]),
     "b200_unary_f32": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64]),
     "b200_transpose_0213_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64]),
+    "b200_maxpool2d_f32": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int64] * 7),
     "b200_transpose_2d_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
 }
 

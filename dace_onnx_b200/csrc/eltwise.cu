@@ -162,6 +162,25 @@ transpose_2d_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int6
   }
 }
 
+// ONNXMaxPool, 2-D, no padding, floor mode: one thread per output element; the kh x kw window is read
+// through L1 (neighbouring threads share its cache lines), so every input byte leaves HBM once.
+__global__ void __launch_bounds__(256)
+maxpool2d_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t planes, int H, int W, int OH, int OW,
+                 int kh, int kw, int sh, int sw) {
+  const int64_t total = planes * OH * OW;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int ow = (int)(i % OW);
+    const int64_t r = i / OW;
+    const int oh = (int)(r % OH);
+    const int64_t plane = r / OH;
+    const float *src = x + (plane * H + (int64_t)oh * sh) * W + (int64_t)ow * sw;
+    float m = -3.402823466e+38f;  // lowest finite float: the initial value of the pure expansion
+    for (int a = 0; a < kh; ++a)
+      for (int b = 0; b < kw; ++b) m = fmaxf(m, __ldg(src + (int64_t)a * W + b));
+    y[i] = m;
+  }
+}
+
 inline unsigned grid_for(int64_t work_items, int threads) {
   int64_t g = (work_items + threads - 1) / threads;
   const int64_t cap = (int64_t)kNumSMs * 16;  // grid-stride loops cover the rest
@@ -301,4 +320,21 @@ extern "C" B200_API int b200_transpose_2d_f32(void *stream, const float *x, floa
   if (batch * rows * cols == 0) return B200_OK;
   if (!x || !y) return fail(B200_EINVAL, "transpose: null pointer");
   return transpose_2d(st, x, y, batch, rows, cols);
+}
+
+extern "C" B200_API int b200_maxpool2d_f32(void *stream, const float *x, float *y, int64_t planes, int64_t H, int64_t W,
+                                  int64_t kh, int64_t kw, int64_t sh, int64_t sw) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (planes < 0 || H < 0 || W < 0) return fail(B200_EINVAL, "maxpool: negative extent");
+  if (kh < 1 || kw < 1 || sh < 1 || sw < 1) return fail(B200_EINVAL, "maxpool: kernel and strides must be positive");
+  if (H > 0x7fffffffLL || W > 0x7fffffffLL || kh > H || kw > W) {
+    if (planes == 0 || H == 0 || W == 0) return B200_OK;
+    return fail(B200_EINVAL, "maxpool: window larger than the image");
+  }
+  const int64_t OH = (H - kh) / sh + 1, OW = (W - kw) / sw + 1;
+  if (planes * OH * OW == 0) return B200_OK;
+  if (!x || !y) return fail(B200_EINVAL, "maxpool: null pointer");
+  maxpool2d_kernel<<<grid_for(planes * OH * OW, 256), 256, 0, st>>>(x, y, planes, (int)H, (int)W, (int)OH, (int)OW,
+                                                                   (int)kh, (int)kw, (int)sh, (int)sw);
+  return check_launch("maxpool2d");
 }

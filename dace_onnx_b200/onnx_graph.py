@@ -180,6 +180,18 @@ def _infer(node: Node, shp, consts):
         oh = (x[2] + pads[0] + pads[2] - dil[0] * (w[2] - 1) - 1) // st[0] + 1
         ow = (x[3] + pads[1] + pads[3] - dil[1] * (w[3] - 1) - 1) // st[1] + 1
         return (x[0], w[0], oh, ow)
+    if op == "MaxPool":
+        x = s[0]
+        ks = node.attr("kernel_shape")
+        pads = node.attr("pads") or [0] * 4
+        if len(x) != 4 or ks is None or len(ks) != 2:
+            raise UnsupportedNode("MaxPool '%s': only 2-D pooling of NCHW tensors" % node.name)
+        if any(pads) or node.attr("ceil_mode", 0) or node.attr("auto_pad", "NOTSET") != "NOTSET" or \
+                any(d != 1 for d in (node.attr("dilations") or [1, 1])) or node.attr("storage_order", 0):
+            raise UnsupportedNode("MaxPool '%s': pads, ceil_mode, dilations and auto_pad are not supported "
+                                  "(as in the reference's pure expansion)" % node.name)
+        st = node.attr("strides") or [1, 1]
+        return (x[0], x[1], (x[2] - ks[0]) // st[0] + 1, (x[3] - ks[1]) // st[1] + 1)
     if op == "ReduceMean":
         x = s[0]
         axes = _axes(node, len(x), list(range(len(x))))

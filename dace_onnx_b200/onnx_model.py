@@ -8,7 +8,7 @@ to an SDFG and expands every node, this class specialises the graph to the input
 buffers once, and then each call only launches kernels of libb200ops on torch's current stream.
 
 Only the node types of the hot path are executable (MatMul, Gemm, Conv, Softmax, LogSoftmax,
-ReduceMean, Add/Sub/Mul/Div/Pow, Sqrt, Erf, Relu, plus Transpose / Reshape-style views between them);
+ReduceMean, Add/Sub/Mul/Div/Pow, Sqrt, Erf, Relu, plus MaxPool and Transpose / Reshape-style views between them);
 anything else raises `UnsupportedNode` when the plan is built - there is no other runtime to fall back on,
 and nothing here computes on the CPU.
 """
@@ -163,6 +163,9 @@ class _Plan:
             return lambda env: ops.matmul(env[ins[0]], env[ins[1]], out=env[out], trans_b=tb, epilogue=epi,
                                           bias=env[ins[2]] if ins[2] else None,
                                           residual=env[ins[3]] if ins[3] else None, scale=scale, math_mode=mm)
+        if op == "MaxPool":
+            ks, st = node.attr("kernel_shape"), node.attr("strides") or [1, 1]
+            return lambda env: ops.maxpool2d(env[ins[0]], ks, st, out=env[out])
         if op == "Gemm":
             return self._gemm_step(node)
         if op == "Conv":

@@ -398,6 +398,23 @@ def transpose_0213(x, out=None):
     return out
 
 
+def maxpool2d(X, kernel_shape, strides=None, out=None):
+    """ONNXMaxPool on NCHW, 2-D windows, no padding (what the pure expansion accepts)."""
+    X = _contig(X, "X")
+    if X.dim() != 4:
+        raise NotImplementedError("MaxPool: only 2-D pooling of NCHW tensors")
+    kh, kw = (int(k) for k in kernel_shape)
+    sh, sw = (int(s) for s in (strides or (1, 1)))
+    n, c, h, w = X.shape
+    if kh > h or kw > w:
+        raise ValueError("MaxPool: window larger than the image")
+    oh, ow = (h - kh) // sh + 1, (w - kw) // sw + 1
+    if out is None:
+        out = torch.empty((n, c, oh, ow), device=X.device, dtype=torch.float32)
+    check(_lib.load().b200_maxpool2d_f32(_stream(), _ptr(X), _ptr(out), n * c, h, w, kh, kw, sh, sw))
+    return out
+
+
 _ONES = {}
 
 

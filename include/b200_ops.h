@@ -203,6 +203,13 @@ B200_API int b200_transpose_0213_f32(void *stream, const float *x, float *y, int
 /* out[c,r] = in[r,c] per batch (ONNXTranspose perm [1,0], the runtime Transpose(W) before MatMul). */
 B200_API int b200_transpose_2d_f32(void *stream, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols);
 
+/* ONNXMaxPool as the reference's pure expansion accepts it (PureMaxPool2D,
+ * daceml/onnx/op_implementations/img_op_implementations.py:29-140): 2-D, pads 0, ceil_mode 0, dilations 1, no Indices
+ * output. x is [planes, H, W] (planes = N*C of an NCHW tensor), y is [planes, (H-kh)/sh+1, (W-kw)/sw+1]. Sits between
+ * the convolutions of the reference's LeNet test (tests/pytorch/test_lenet.py:14-32). */
+B200_API int b200_maxpool2d_f32(void *stream, const float *x, float *y, int64_t planes, int64_t H, int64_t W,
+                                int64_t kh, int64_t kw, int64_t sh, int64_t sw);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,6 +44,8 @@ def run(model, inputs):
         elif op == "Conv":
             y = po.Conv(i[0], i[1], i[2] if len(i) > 2 else None, tuple(n.attr("pads", [0, 0, 0, 0])),
                         tuple(n.attr("strides", [1, 1])))
+        elif op == "MaxPool":
+            y = po.MaxPool(i[0], n.attr("kernel_shape"), n.attr("strides") or [1, 1])
         elif op == "Softmax":
             y = po.Softmax(i[0], n.attr("axis", 1))
         elif op == "LogSoftmax":

@@ -168,6 +168,22 @@ def Conv(X, W, B=None, pads=(0, 0, 0, 0), strides=(1, 1)):
     return y
 
 
+def MaxPool(X, kernel_shape, strides=(1, 1)):
+    """daceml/onnx/op_implementations/img_op_implementations.py:29-140 (PureMaxPool2D): pads 0, ceil_mode 0,
+    dilations 1; Y starts at the lowest value of the dtype (:90-104) and a map over (b, c, out_x, out_y, hx, hy)
+    takes the maximum of X[b, c, stride_x*out_x + hx, stride_y*out_y + hy] into it."""
+    x = _t(X)
+    kh, kw = int(kernel_shape[0]), int(kernel_shape[1])
+    sh, sw = int(strides[0]), int(strides[1])
+    n, c, h, w = x.shape
+    oh, ow = (h - kh) // sh + 1, (w - kw) // sw + 1
+    y = torch.full((n, c, oh, ow), torch.finfo(F32).min, dtype=F32)
+    for hx in range(kh):
+        for hy in range(kw):
+            y = torch.maximum(y, x[:, :, hx:hx + (oh - 1) * sh + 1:sh, hy:hy + (ow - 1) * sw + 1:sw])
+    return y
+
+
 # ---------------------------------------------------------------------------------------------
 # node chains that opset-12 export produces for LayerNorm and Gelu
 # ---------------------------------------------------------------------------------------------

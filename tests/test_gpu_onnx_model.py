@@ -134,3 +134,50 @@ def test_cuda_graph_replay_equals_eager(name, cuda):
     buf = model.static_inputs(x.shape)[0]
     buf.copy_(x)
     assert torch.equal(model(buf), eager)
+
+
+@pytest.mark.parametrize("kernel,stride,shape", [((2, 2), (2, 2), (8, 6, 30, 30)), ((3, 3), (1, 1), (2, 3, 9, 11)),
+                                                 ((2, 3), (3, 2), (1, 4, 17, 13)), ((2, 2), (2, 2), (64, 16, 56, 56))])
+def test_maxpool_node(kernel, stride, shape, cuda):
+    from oracle import pure_oracle as po
+    x = torch.randn(*shape, generator=torch.Generator().manual_seed(41))
+    assert torch.equal(ops.maxpool2d(x.cuda(), kernel, stride).cpu(), po.MaxPool(x, kernel, stride))
+    assert ops.maxpool2d(torch.empty(0, 3, 8, 8, device="cuda"), (2, 2), (2, 2)).shape == (0, 3, 4, 4)
+    with pytest.raises(ValueError):
+        ops.maxpool2d(x.cuda()[:, :, :1], (2, 2))
+
+
+def test_lenet_like_the_reference_test(cuda):
+    """tests/pytorch/test_lenet.py:14-54 with B200Module in place of DaceModule and the same comparator."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    class LeNet(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv1 = nn.Conv2d(1, 6, (3, 3))
+            self.conv2 = nn.Conv2d(6, 16, (3, 3))
+            self.fc1 = nn.Linear(16 * 6 * 6, 120)
+            self.fc2 = nn.Linear(120, 84)
+            self.fc3 = nn.Linear(84, 10)
+
+        def forward(self, x):
+            x = F.max_pool2d(F.relu(self.conv1(x)), 2)
+            x = F.max_pool2d(F.relu(self.conv2(x)), 2)
+            x = x.view(-1, 16 * 6 * 6)
+            x = F.relu(self.fc1(x))
+            x = F.relu(self.fc2(x))
+            return F.log_softmax(self.fc3(x), dim=1)
+
+    torch.manual_seed(11)
+    net = LeNet().eval()
+    x = torch.rand(8, 1, 32, 32)
+    with torch.no_grad():
+        ref = net(x)
+    for fuse in (True, False):
+        mod = B200Module(net, fuse=fuse, sdfg_name="lenet")
+        out = mod(x)
+        close(out, ref, REF_RTOL, REF_ATOL)
+        close(out, graph_oracle.run(export_onnx(net, (x,)), [x])[0], RTOL, ATOL)
+    hist = B200Module(net, dummy_inputs=(x,)).onnx_model.plan((8, 1, 32, 32)).ir.op_histogram()
+    assert hist == {"Conv": 2, "MaxPool": 2, "Reshape": 1, "B200Gemm": 3, "LogSoftmax": 1}

@@ -183,3 +183,12 @@ def test_golden_conv(name):
     ref = torch.nn.functional.conv2d(torch.tensor(g["X"]).double(), torch.tensor(g["W"]).double(),
                                      None if B is None else B.double(), padding=pad)
     assert np.allclose(g["Y"], ref.numpy(), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("kernel,stride,shape", [((2, 2), (2, 2), (8, 6, 30, 30)), ((3, 3), (1, 1), (2, 3, 9, 11)),
+                                                 ((2, 3), (3, 2), (1, 4, 17, 13))])
+def test_maxpool_matches_torch(kernel, stride, shape):
+    """PureMaxPool2D (pads 0, floor mode); the reference pins it through its LeNet test
+    (tests/pytorch/test_lenet.py:14-54) against F.max_pool2d."""
+    x = torch.randn(*shape, generator=torch.Generator().manual_seed(40))
+    assert torch.equal(po.MaxPool(x, kernel, stride), torch.nn.functional.max_pool2d(x, kernel, stride))
