@@ -182,6 +182,17 @@ def conv_env_code(x_shape, w_shape, pads, strides, ws_name, mode=None):
     return fields, init, fini
 
 
+def tasklet_maxpool(x_shape, kernel_shape, strides, label="MaxPool"):
+    """Body for MaxPool (X -> Y), 2-D, pads 0, floor mode (the cases PureMaxPool2D accepts,
+    img_op_implementations.py:31-61)."""
+    n, c, h, w = [int(s) for s in x_shape]
+    kh, kw = [int(k) for k in kernel_shape]
+    sh, sw = [int(s) for s in (strides or [1, 1])]
+    return """
+    int __b200_rc = b200_maxpool2d_f32(__dace_current_stream, _X, _Y, {planes}, {h}, {w}, {kh}, {kw}, {sh}, {sw});
+""".format(planes=n * c, h=h, w=w, kh=kh, kw=kw, sh=sh, sw=sw) + CHECK.format(label=label)
+
+
 def _axis_view(shape, axis):
     nd = len(shape)
     axis = int(axis) % nd
@@ -353,6 +364,12 @@ def _register():
          node.auto_pad == "NOTSET" and (node.dilations is None or all(x == 1 for x in node.dilations)) and
          (node.pads is None or (node.pads[0] == node.pads[2] and node.pads[1] == node.pads[3])),
          conv_build)
+    make("MaxPool", ["X"], ["Y"],
+         lambda node, d: len(d["X"].shape) == 4 and len(node.kernel_shape) == 2 and
+         (node.pads is None or all(p == 0 for p in node.pads)) and node.auto_pad == "NOTSET" and
+         node.ceil_mode == 0 and node.storage_order == 0 and
+         (node.dilations is None or all(x == 1 for x in node.dilations)),
+         lambda node, d: (tasklet_maxpool(d["X"].shape, node.kernel_shape, node.strides, node.label), None))
     make("Softmax", ["input"], ["output"], lambda node, d: True,
          lambda node, d: (tasklet_softmax(d["input"].shape, node.axis, False, node.label), None))
     make("LogSoftmax", ["input"], ["output"], lambda node, d: True,

@@ -35,6 +35,7 @@ def bodies():
         impl.tasklet_matmul((64, 512, 768), (768, 768), mode=0, ws="ws"),
         impl.tasklet_matmul((4096, 784), (120, 784), trans_b=True, bias=True, mode=0, ws="ws"),
         impl.tasklet_conv((256, 64, 56, 56), (64, 64, 3, 3), (1, 1, 1, 1), (1, 1), True, mode=0).replace("{ws}", "ws"),
+        impl.tasklet_maxpool((8, 6, 30, 30), (2, 2), (2, 2)),
         impl.tasklet_softmax((768, 512, 512), -1),
         impl.tasklet_softmax((2, 4, 10), 0, log=True),
         impl.tasklet_reduce_mean((32768, 768), [-1]),
