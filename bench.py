@@ -408,14 +408,14 @@ def kernel_cases(device):
             return (lambda: enc.forward_device(x, out=y)), flops, 0, "tensor"
         return make
 
-    def frontdoor_mlp_c1(cuda_graph=False):
+    def frontdoor_mlp_c1(cuda_graph=False, mode="fp32x3"):
         # configuration 1: Linear 784-120-32-10 + ReLU + LogSoftmax, batch 4096, exported and run from the graph
         def make():
             from dace_onnx_b200.torch_module import B200Module
             torch.manual_seed(0)
             net = torch.nn.Sequential(torch.nn.Linear(784, 120), torch.nn.ReLU(), torch.nn.Linear(120, 32),
                                       torch.nn.ReLU(), torch.nn.Linear(32, 10), torch.nn.LogSoftmax(dim=1)).eval()
-            mod = B200Module(net, dummy_inputs=(torch.zeros(4096, 784),), math_mode="fp32x3", cuda_graph=cuda_graph)
+            mod = B200Module(net, dummy_inputs=(torch.zeros(4096, 784),), math_mode=mode, cuda_graph=cuda_graph)
             x = rn(4096, 784)
             if cuda_graph:  # the serving pattern: fill the captured input buffer in place, replay
                 mod(x)
@@ -427,6 +427,8 @@ def kernel_cases(device):
         "frontdoor_bert_large_layer_tf32": frontdoor_bert_layer(64, 384, 1024, 16, 4096, "tf32"),
         "encoder_bert_large_layer_tf32": encoder_bert_layer(64, 384, 1024, 16, 4096, "tf32"),
         "frontdoor_mlp_c1": frontdoor_mlp_c1(), "frontdoor_mlp_c1_cudagraph": frontdoor_mlp_c1(True),
+        "frontdoor_mlp_c1_cudagraph_fp32": frontdoor_mlp_c1(True, "fp32"),
+        "frontdoor_mlp_c1_cudagraph_tf32": frontdoor_mlp_c1(True, "tf32"),
         "conv_c2_fp32x3": conv(256, 64, 56, 64, "fp32x3"), "conv_c2_tf32": conv(256, 64, 56, 64, "tf32"),
         "softmax_c4": softmax_c4, "layernorm_c4": layernorm_c4,
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),

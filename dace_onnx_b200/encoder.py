@@ -9,7 +9,7 @@ the contraction epilogues where the graph allows it:
     ... + Add(residual)                                      -> EPI_BIAS_RESIDUAL
     ... + Div/Erf/Add/Mul/Mul (Gelu)                         -> EPI_BIAS_GELU
     MatMul(q, k^T), Mul(1/sqrt(d)), Softmax, MatMul(p, v)    -> one fused attention kernel (TF32 mode,
-                                                                head_dim 64, seq <= 384); otherwise:
+                                                                head_dim 64, seq % 32 == 0); otherwise:
     MatMul(q, k^T) + Mul(1/sqrt(d))                          -> batched gemm, EPI_SCALE
     Reshape/Transpose [0,2,1,3] either side of attention     -> strided batch addressing (no copy)
     ReduceMean..Add (9 nodes)                                -> layernorm

@@ -116,7 +116,7 @@ B200_API int b200_gemm_ws_f32(void *stream, const b200_gemm_desc *desc, const fl
  * pure_implementations.py:130-235, :87-89, :346-366) without writing the [seq, seq] scores to memory.
  * Q, K, V, out are [batch, seq, heads, head_dim] views given by element strides per row (token),
  * head and batch, head_dim contiguous -- e.g. slices of a fused QKV projection, and out laid out as
- * [batch, seq, hidden]. Implemented for math_mode TF32, head_dim 64, seq a multiple of 32 up to 384,
+ * [batch, seq, hidden]. Implemented for math_mode TF32, head_dim 64, seq a multiple of 32 (any length),
  * scale > 0, 16-byte aligned Q/K/V with strides that are multiples of 4 and a 32-byte aligned out
  * with strides that are multiples of 8; b200_attention_supported() says whether a call qualifies,
  * anything else returns B200_EUNSUPPORTED and the caller runs the unfused nodes. */
