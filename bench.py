@@ -26,6 +26,7 @@ WORKLOADS = {
     # name: (layers, hidden, heads, ffn, batch, seq, math mode)
     "bert_large_x24_b1024_s384_tf32": (24, 1024, 16, 4096, 1024, 384, "tf32"),
     "bert_base_x1_b64_s512_fp32x3": (1, 768, 12, 3072, 64, 512, "fp32x3"),
+    "bert_base_x1_b64_s512_tf32": (1, 768, 12, 3072, 64, 512, "tf32"),
 }
 DEFAULT_WORKLOAD = "bert_large_x24_b1024_s384_tf32"
 METRIC = "bert_encoder_seqs_per_s"
@@ -437,6 +438,7 @@ def kernel_cases(device):
         "gemm_fp32x3_ffn1_no_workspace": gemm_no_workspace(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
         "attention_fused_tf32": attn_fused(32, 16, 384, 64),
+        "attention_stream_tf32_s512": attn_fused(64, 12, 512, 64), "attention_stream_tf32_s2048": attn_fused(8, 16, 2048, 64),
         "attention_fused_tf32_headmajor": attn_fused_headmajor(32, 16, 384, 64),
     }
 

@@ -297,7 +297,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // tiles of this CTA): QK(0), QK(1), PV(0), QK(2), PV(1), ... - the loads follow the same order.
 //   s_full[2]  issuer -> softmax: scores of block g are in buffer g % 2
 //   p_full[2]  softmax (256 arrivals) -> issuer: P of block g written (and O rescaled)
-//   pv         issuer -> softmax: P_g V_g has been accumulated (one completion per block)
+//   pv[2]      issuer -> softmax: P_g V_g has been accumulated (barrier g % 2; two, because the softmax warps
+//              only wait for it when they must rescale O or read it out, and a single barrier could then be
+//              two phases ahead of a waiter's parity)
 //   o_empty    softmax (256) -> issuer: the tile's output has been read, O may be overwritten
 // ---------------------------------------------------------------------------------------------
 constexpr int kFlashOCol = 256;
@@ -320,7 +322,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_q_full = bar0, bar_q_empty = bar0 + 16, bar_ring_full = bar0 + 32,
                  bar_ring_empty = bar_ring_full + 8 * kRing, bar_s_full = bar_ring_empty + 8 * kRing,
-                 bar_p_full = bar_s_full + 16, bar_pv = bar_p_full + 16, bar_o_empty = bar_pv + 8;
+                 bar_p_full = bar_s_full + 16, bar_pv = bar_p_full + 16, bar_o_empty = bar_pv + 16;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_red[2][128];
@@ -333,12 +335,12 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_init(bar_q_empty + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
       mbar_init(bar_p_full + 8 * i, 256);
+      mbar_init(bar_pv + 8 * i, 1);
     }
     for (int i = 0; i < kRing; ++i) {
       mbar_init(bar_ring_full + 8 * i, 1);
       mbar_init(bar_ring_empty + 8 * i, 1);
     }
-    mbar_init(bar_pv, 1);
     mbar_init(bar_o_empty, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -454,7 +456,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         umma_commit(bar_ring_empty + 8 * rs);
         if (++rs == kRing) { rs = 0; r_ph ^= 1; }
-        umma_commit(bar_pv);
+        umma_commit(bar_pv + 8 * (uint32_t)(g & 1));
         pv.next(nb);
       }
     }
@@ -492,10 +494,15 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       s_red[half][row_in_tile] = m_loc;
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      const float m_new = fmaxf(m_run, fmaxf(m_loc, s_red[half ^ 1][row_in_tile]));
+      const float m_blk = fmaxf(m_loc, s_red[half ^ 1][row_in_tile]);
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      float alpha;  // exp((m_run - m_new) * scale): the factor by which earlier blocks' terms shrink
-      asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"((m_run - m_new) * c));
+      // The exponent offset only follows the running maximum when that has grown by more than 2^8 (in the
+      // exp2 domain): P then stays below 256 instead of 1, which fp32 / TF32 hold just as well, and the
+      // rescaling of O - with its wait for the previous block's P V - becomes rare.
+      const bool grow = bi.j == 0 || (m_blk - m_run) * c > 8.0f;
+      const float m_new = grow ? m_blk : m_run;
+      float alpha = 1.0f;  // exp((m_run - m_new) * scale): the factor by which earlier blocks' terms shrink
+      if (grow) asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(alpha) : "f"((m_run - m_new) * c));
       if (bi.j == 0) alpha = 0.f;
       const float off = m_new * c;
       float sum = 0.f;
@@ -521,12 +528,14 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
       l_run = l_run * alpha + sum;
       m_run = m_new;
-      if (bi.j > 0) {
-        // O holds sum_{i<j} P_i V_i relative to the old maximum: wait for P_{j-1} V_{j-1}, then rescale this
-        // thread's 32 output columns (skipped when no row of the warp moved its maximum)
-        if (!(ok = mbar_wait(bar_pv, (uint32_t)((g - 1) & 1), abort_flag, p.status, 8u))) break;
+      if (bi.j > 0 && __any_sync(0xffffffffu, grow)) {
+        // O holds sum_{i<j} P_i V_i relative to the old offset: wait for P_{j-1} V_{j-1}, then rescale this
+        // thread's 32 output columns (rows of the warp that kept their offset multiply by 1)
+        if (!(ok = mbar_wait(bar_pv + 8 * (uint32_t)((g - 1) & 1), (uint32_t)(((g - 1) >> 1) & 1), abort_flag, p.status,
+                             8u)))
+          break;
         tc_fence_after();
-        if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+        {
           uint32_t o[32];
           tmem_ld32(lane_addr + kFlashOCol + half * 32, o);
           tmem_ld_wait();
@@ -545,7 +554,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         const float l_tot = l_run + s_red[half ^ 1][row_in_tile];
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        if (!(ok = mbar_wait(bar_pv, (uint32_t)(g & 1), abort_flag, p.status, 8u))) break;
+        if (!(ok = mbar_wait(bar_pv + 8 * (uint32_t)(g & 1), (uint32_t)((g >> 1) & 1), abort_flag, p.status, 8u))) break;
         tc_fence_after();
         const int64_t item = blockIdx.x + (int64_t)bi.it * gridDim.x;
         const int b = (int)(item / p.heads), h = (int)(item % p.heads);
@@ -641,7 +650,12 @@ int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, 
   const int64_t grid = p.items < kNumSMs ? p.items : kNumSMs;
   // Rows of up to 384 scores stay resident in TMEM (two-pass softmax, measured 239 against 201 TFLOP/s at S = 384:
   // the streaming form pays a P V -> rescale -> P V dependency per key block); longer rows stream.
-  if (d.seq <= kMaxS) {
+#ifndef B200_ATTENTION_ALWAYS_STREAM  // build-time switch for comparing the two kernels on sequences both can run
+  if (d.seq <= kMaxS)
+#else
+  if (false)
+#endif
+  {
     attention_tc_kernel<<<(unsigned)grid, kThreads, smem, st>>>(mq, mk, mv, p);
     return check_launch("attention_tc");
   }
