@@ -1,7 +1,8 @@
 // Fused attention for sm_100a: softmax(Q K^T * scale) V per (batch, head) without materialising
-// the [S, S] score matrix in HBM. Two kernels: attention_tc_kernel keeps a query tile's whole score rows in
-// TMEM (S <= 384); attention_stream_kernel (further down) walks the keys in blocks with a running maximum (any S). Replaces the node pattern MatMul -> Mul(const) -> Softmax ->
-// MatMul of the exported BERT graph (TF32 tensor-core mode).
+// the [S, S] score matrix in HBM. Replaces the node pattern MatMul -> Mul(const) -> Softmax -> MatMul of the
+// exported BERT graph (TF32 tensor-core mode). Two kernels: attention_tc_kernel, described here, keeps a query
+// tile's whole score rows in TMEM (S <= 384); attention_stream_kernel (further down) walks the keys in blocks
+// with a running maximum (any S).
 //
 // One persistent CTA per SM walks (batch, head) items, 128 query rows at a time. Q is double
 // buffered; the head's K and V stream through a ring of 128-row blocks (K as the K-major B operand
@@ -290,19 +291,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 // ---------------------------------------------------------------------------------------------
 // Streaming variant: key / value blocks of 128 are consumed one at a time with a running row maximum
 // and row sum (the softmax of the exported graph, evaluated block by block: P_j = exp(s - m_j) with
-// m_j the maximum so far, O and the row sum rescaled by exp(m_{j-1} - m_j) when the maximum moves).
-// Scores use two alternating 128-column TMEM buffers, so the tensor core computes Q K_{j+1}^T while
-// the softmax warps work on block j, and P_j V_j while they work on block j+1; TMEM use no longer
-// depends on the sequence length. Issue order of the MMA thread (g = running block index over all
-// tiles of this CTA): QK(0), QK(1), PV(0), QK(2), PV(1), ... - the loads follow the same order.
-//   s_full[2]  issuer -> softmax: scores of block g are in buffer g % 2
-//   p_full[2]  softmax (256 arrivals) -> issuer: P of block g written (and O rescaled)
-//   pv[2]      issuer -> softmax: P_g V_g has been accumulated (barrier g % 2; two, because the softmax warps
-//              only wait for it when they must rescale O or read it out, and a single barrier could then be
-//              two phases ahead of a waiter's parity)
-//   o_empty    softmax (256) -> issuer: the tile's output has been read, O may be overwritten
+// m_j the exponent offset so far, O and the row sum rescaled by exp(m_{j-1} - m_j) when the offset moves),
+// so TMEM use does not depend on the sequence length.
 // ---------------------------------------------------------------------------------------------
-constexpr int kFlashOCol = 256;
 
 struct BlkIter {
   int it, mt, j;  // this CTA's item counter, query tile, key block
@@ -311,18 +302,33 @@ struct BlkIter {
   }
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+// ---------------------------------------------------------------------------------------------
+// Several MMA-issuing threads: one thread issuing every tcgen05.mma of a key block (8 for the scores, 16 for
+// P V, ~90-130 clk each; measured with clock64()) needs ~3000 clk per block - more than the softmax warps
+// (~1650) or the tensor core. Here warp 1 issues the scores and warps 10 and 11 the P V products
+// (half the keys of a block each, into two partial output accumulators that are added at the end), the
+// scores rotate through three 128-column TMEM buffers (so the score thread runs up to three blocks
+// ahead of P V), and keys and values have rings of their own. The exponent offset follows the running
+// maximum lazily (only when that has grown by more than 2^8), so rescaling O is rare.
+//   s_full[3]  A -> softmax      p_full[3]  softmax (256) -> B      pv[3]  B -> A (buffer free), softmax
+//   k_full/k_empty[3], v_full/v_empty[2], q_full/q_empty[2]: loads    o_empty  softmax (256) -> B
+// ---------------------------------------------------------------------------------------------
+constexpr int kThreads2 = 32 * 12;  // producer, issuer A, 8 softmax / output warps, issuers B1 and B2
+constexpr int kOColA = 384, kOColB = 448;  // the two partial output accumulators (B1: first 64 keys of a block, B2: rest)
+
+__global__ void __launch_bounds__(kThreads2, 1)
 attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t q_smem = smem_u32(smem);
-  const uint32_t ring_smem = q_smem + 2 * kBlkBytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (2 + kRing) * (size_t)kBlkBytes);
+  const uint32_t k_smem = q_smem + 2 * kBlkBytes;          // three key blocks (issuer A's ring)
+  const uint32_t v_smem = k_smem + 3 * kBlkBytes;          // two value blocks (issuer B's ring)
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 7 * (size_t)kBlkBytes);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t bar_q_full = bar0, bar_q_empty = bar0 + 16, bar_ring_full = bar0 + 32,
-                 bar_ring_empty = bar_ring_full + 8 * kRing, bar_s_full = bar_ring_empty + 8 * kRing,
-                 bar_p_full = bar_s_full + 16, bar_pv = bar_p_full + 16, bar_o_empty = bar_pv + 16;
+  const uint32_t bar_q_full = bar0, bar_q_empty = bar0 + 16, bar_k_full = bar0 + 32, bar_k_empty = bar0 + 56,
+                 bar_v_full = bar0 + 80, bar_v_empty = bar0 + 96, bar_s_full = bar0 + 112, bar_p_full = bar0 + 136,
+                 bar_pv = bar0 + 160, bar_o_empty = bar0 + 184;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ float s_red[2][128];
@@ -333,13 +339,15 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_q_full + 8 * i, 1);
       mbar_init(bar_q_empty + 8 * i, 1);
+      mbar_init(bar_v_full + 8 * i, 1);
+      mbar_init(bar_v_empty + 8 * i, 2);  // both P V issuers release a value block
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(bar_k_full + 8 * i, 1);
+      mbar_init(bar_k_empty + 8 * i, 1);
       mbar_init(bar_s_full + 8 * i, 1);
       mbar_init(bar_p_full + 8 * i, 256);
-      mbar_init(bar_pv + 8 * i, 1);
-    }
-    for (int i = 0; i < kRing; ++i) {
-      mbar_init(bar_ring_full + 8 * i, 1);
-      mbar_init(bar_ring_empty + 8 * i, 1);
+      mbar_init(bar_pv + 8 * i, 2);       // both halves of P_g V_g
     }
     mbar_init(bar_o_empty, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -359,104 +367,130 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
+    // Key blocks go to a ring of three (consumed by the score issuer, which runs up to three blocks ahead),
+    // value blocks to a ring of two (consumed by the P V issuer): K_0 K_1 K_2, then V_g, K_{g+3} for every g.
     if (lane == 0) {
-      int rs = 0, qs = 0;
-      uint32_t r_ph = 0, q_ph = 0;
+      int qs = 0;
+      uint32_t q_ph = 0;
       bool ok = true;
-      auto load_block = [&](const CUtensorMap *map, int r0, int h, int b) {
-        if (!(ok = mbar_wait(bar_ring_empty + 8 * rs, r_ph ^ 1, abort_flag, p.status, 1u))) return;
-        mbar_expect_tx(bar_ring_full + 8 * rs, kBlkBytes);
-        const uint32_t dst = ring_smem + rs * kBlkBytes;
-        tma_load_4d(dst, map, bar_ring_full + 8 * rs, 0, r0, h, b);
-        tma_load_4d(dst + kBlkBytes / 2, map, bar_ring_full + 8 * rs, 32, r0, h, b);
-        if (++rs == kRing) { rs = 0; r_ph ^= 1; }
+      auto coords = [&](const BlkIter &x, int &b, int &h) {
+        const int64_t item = blockIdx.x + (int64_t)x.it * gridDim.x;
+        b = (int)(item / p.heads);
+        h = (int)(item % p.heads);
       };
-      auto load_k = [&](const BlkIter &k) {  // the key block, preceded by the tile's Q when it is the tile's first
-        const int64_t item = blockIdx.x + (int64_t)k.it * gridDim.x;
-        const int b = (int)(item / p.heads), h = (int)(item % p.heads);
-        if (k.j == 0) {
+      auto load_k = [&](const BlkIter &x, int64_t g) {
+        int b, h;
+        coords(x, b, h);
+        if (x.j == 0) {
           if (!(ok = mbar_wait(bar_q_empty + 8 * qs, q_ph ^ 1, abort_flag, p.status, 1u))) return;
           mbar_expect_tx(bar_q_full + 8 * qs, kBlkBytes);
-          tma_load_4d(q_smem + qs * kBlkBytes, &map_q, bar_q_full + 8 * qs, 0, k.mt * 128, h, b);
-          tma_load_4d(q_smem + qs * kBlkBytes + kBlkBytes / 2, &map_q, bar_q_full + 8 * qs, 32, k.mt * 128, h, b);
+          tma_load_4d(q_smem + qs * kBlkBytes, &map_q, bar_q_full + 8 * qs, 0, x.mt * 128, h, b);
+          tma_load_4d(q_smem + qs * kBlkBytes + kBlkBytes / 2, &map_q, bar_q_full + 8 * qs, 32, x.mt * 128, h, b);
           if (++qs == 2) { qs = 0; q_ph ^= 1; }
         }
-        load_block(&map_k, k.j * 128, h, b);
+        const uint32_t slot = (uint32_t)(g % 3), full = bar_k_full + 8 * slot;
+        if (!(ok = mbar_wait(bar_k_empty + 8 * slot, (uint32_t)((g / 3) & 1) ^ 1, abort_flag, p.status, 1u))) return;
+        mbar_expect_tx(full, kBlkBytes);
+        tma_load_4d(k_smem + slot * kBlkBytes, &map_k, full, 0, x.j * 128, h, b);
+        tma_load_4d(k_smem + slot * kBlkBytes + kBlkBytes / 2, &map_k, full, 32, x.j * 128, h, b);
       };
       BlkIter kq{0, 0, 0}, v{0, 0, 0};
-      if (G > 0) { load_k(kq); kq.next(nb); }
+      int64_t gk = 0;
+      for (; gk < 3 && gk < G && ok; ++gk) { load_k(kq, gk); kq.next(nb); }
       for (int64_t g = 0; g < G && ok; ++g) {
-        if (kq.it < n_my) { load_k(kq); kq.next(nb); }
-        if (!ok) break;
-        const int64_t item = blockIdx.x + (int64_t)v.it * gridDim.x;
-        load_block(&map_v, v.j * 128, (int)(item % p.heads), (int)(item / p.heads));
+        int b, h;
+        coords(v, b, h);
+        const uint32_t slot = (uint32_t)(g & 1), full = bar_v_full + 8 * slot;
+        if (!(ok = mbar_wait(bar_v_empty + 8 * slot, (uint32_t)((g >> 1) & 1) ^ 1, abort_flag, p.status, 1u))) break;
+        mbar_expect_tx(full, kBlkBytes);
+        tma_load_4d(v_smem + slot * kBlkBytes, &map_v, full, 0, v.j * 128, h, b);
+        tma_load_4d(v_smem + slot * kBlkBytes + kBlkBytes / 2, &map_v, full, 32, v.j * 128, h, b);
         v.next(nb);
+        if (gk < G) { load_k(kq, gk); kq.next(nb); ++gk; }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+    // ------------------------------- issuer A: scores -------------------------------
+    // S_g = Q K_g^T into score buffer g % 3, as soon as P V_{g-3} has consumed what that buffer held.
     if (lane == 0) {
-      int rs = 0, qs = 0;
-      uint32_t r_ph = 0, q_ph = 0;
-      const uint32_t idesc_o = make_idesc(kD, true);
+      int qs = 0;
+      uint32_t q_ph = 0;
       const uint32_t idesc_full = make_idesc(128, false);
       const uint64_t kdesc0 = make_smem_desc(0, 16, 1024, kLayoutSw128);
-      const uint64_t vdesc0 = make_smem_desc(0, kBlkBytes / 2, 512, kLayoutSw128Base32);
       bool ok = true;
-      int64_t gk = 0;  // running index of the block whose scores are issued next
-      auto issue_qk = [&](const BlkIter &k) {
-        if (k.j == 0) {
-          if (!(ok = mbar_wait(bar_q_full + 8 * qs, q_ph, abort_flag, p.status, 2u))) return;
+      BlkIter kq{0, 0, 0};
+      for (int64_t g = 0; g < G && ok; ++g) {
+        const uint32_t sb = (uint32_t)(g % 3), sp = (uint32_t)((g / 3) & 1);
+        if (g >= 3) {
+          if (!(ok = mbar_wait(bar_pv + 8 * sb, sp ^ 1, abort_flag, p.status, 2u))) break;  // completion g/3 - 1
         }
-        if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 2u))) return;
+        if (kq.j == 0) {
+          if (!(ok = mbar_wait(bar_q_full + 8 * qs, q_ph, abort_flag, p.status, 2u))) break;
+        }
+        if (!(ok = mbar_wait(bar_k_full + 8 * sb, sp, abort_flag, p.status, 2u))) break;
         tc_fence_after();
-        const int n_len = p.S - k.j * 128;
+        const int n_len = p.S - kq.j * 128;
         const uint32_t idesc_s = n_len >= 128 ? idesc_full : make_idesc(n_len, false);
         const uint64_t a_base = kdesc0 + ((q_smem + qs * kBlkBytes) >> 4);
-        const uint64_t b_base = kdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
-        const uint32_t d_tmem = tmem_base + (uint32_t)(gk & 1) * 128;
+        const uint64_t b_base = kdesc0 + ((k_smem + sb * kBlkBytes) >> 4);
+        const uint32_t d_tmem = tmem_base + sb * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           constexpr uint32_t kHalf = (kBlkBytes / 2) >> 4;
           const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 2;
           umma_tf32(d_tmem, a_base + off, b_base + off, idesc_s, ks > 0 ? 1u : 0u);
         }
-        umma_commit(bar_ring_empty + 8 * rs);
-        if (++rs == kRing) { rs = 0; r_ph ^= 1; }
-        umma_commit(bar_s_full + 8 * (uint32_t)(gk & 1));
-        if (k.j == nb - 1) {  // the tile's last score block: its Q buffer is free once these MMAs are done
+        umma_commit(bar_k_empty + 8 * sb);
+        umma_commit(bar_s_full + 8 * sb);
+        if (kq.j == nb - 1) {
           umma_commit(bar_q_empty + 8 * qs);
           if (++qs == 2) { qs = 0; q_ph ^= 1; }
         }
-        ++gk;
-      };
-      BlkIter kq{0, 0, 0}, pv{0, 0, 0};
-      int64_t tile = 0;  // tiles whose P V has been started
-      if (G > 0) { issue_qk(kq); kq.next(nb); }
+        kq.next(nb);
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------- issuers B1 / B2: O += P_g V_g -------------------------------
+    // Warp 10 multiplies the first 64 keys of every block into accumulator A, warp 11 the remaining keys into
+    // accumulator B (two threads issue the N = 64 instructions faster than one; the output is A + B).
+    if (lane == 0) {
+      const int second = warp - 10;
+      const uint32_t o_tmem = tmem_base + (second ? kOColB : kOColA);
+      const uint32_t idesc_o = make_idesc(kD, true);
+      const uint64_t vdesc0 = make_smem_desc(0, kBlkBytes / 2, 512, kLayoutSw128Base32);
+      bool ok = true;
+      BlkIter pv{0, 0, 0};
+      int64_t tile = 0;
+      uint32_t started = 0;  // 0 until this accumulator has received its first product of the tile
       for (int64_t g = 0; g < G && ok; ++g) {
-        if (kq.it < n_my) { issue_qk(kq); kq.next(nb); }
-        if (!ok) break;
+        const uint32_t sb = (uint32_t)(g % 3), sp = (uint32_t)((g / 3) & 1), vs = (uint32_t)(g & 1);
         if (pv.j == 0) {  // the previous tile's output must have been read before O is overwritten
-          if (!(ok = mbar_wait(bar_o_empty, (uint32_t)(tile & 1) ^ 1, abort_flag, p.status, 2u))) break;
+          if (!(ok = mbar_wait(bar_o_empty, (uint32_t)(tile & 1) ^ 1, abort_flag, p.status, 4u))) break;
           ++tile;
+          started = 0;
         }
-        if (!(ok = mbar_wait(bar_p_full + 8 * (uint32_t)(g & 1), (uint32_t)((g >> 1) & 1), abort_flag, p.status, 4u))) break;
-        if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 4u))) break;
+        if (!(ok = mbar_wait(bar_p_full + 8 * sb, sp, abort_flag, p.status, 4u))) break;
+        if (!(ok = mbar_wait(bar_v_full + 8 * vs, (uint32_t)((g >> 1) & 1), abort_flag, p.status, 4u))) break;
         tc_fence_after();
-        const uint64_t v_base = vdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
-        const uint32_t p_tmem = tmem_base + (uint32_t)(g & 1) * 128;
+        const uint64_t v_base = vdesc0 + ((v_smem + vs * kBlkBytes) >> 4);
+        const uint32_t p_tmem = tmem_base + sb * 128;
         const int k_len = p.S - pv.j * 128 < 128 ? p.S - pv.j * 128 : 128;
-        if (k_len == 128) {
+        const int k8_lo = second ? 8 : 0, k8_hi = second ? k_len / 8 : (k_len / 8 < 8 ? k_len / 8 : 8);
+        if (k8_hi - k8_lo == 8) {
 #pragma unroll
-          for (int k8 = 0; k8 < 16; ++k8)
-            umma_tf32_ts(tmem_base + kFlashOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (pv.j > 0 || k8 > 0) ? 1u : 0u);
+          for (int q = 0; q < 8; ++q) {
+            const int k8 = k8_lo + q;
+            umma_tf32_ts(o_tmem, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, q > 0 ? 1u : started);
+          }
+          started = 1;
         } else {
-          for (int k8 = 0; k8 * 8 < k_len; ++k8)
-            umma_tf32_ts(tmem_base + kFlashOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (pv.j > 0 || k8 > 0) ? 1u : 0u);
+          for (int k8 = k8_lo; k8 < k8_hi; ++k8) {
+            umma_tf32_ts(o_tmem, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, started);
+            started = 1;
+          }
         }
-        umma_commit(bar_ring_empty + 8 * rs);
-        if (++rs == kRing) { rs = 0; r_ph ^= 1; }
-        umma_commit(bar_pv + 8 * (uint32_t)(g & 1));
+        umma_commit(bar_v_empty + 8 * vs);
+        umma_commit(bar_pv + 8 * sb);
         pv.next(nb);
       }
     }
@@ -474,10 +508,11 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     BlkIter bi{0, 0, 0};
     float m_run = -INFINITY, l_run = 0.f;
     for (int64_t g = 0; g < G && ok; ++g) {
-      const uint32_t s_addr = lane_addr + (uint32_t)(g & 1) * 128 + half * 64;
+      const uint32_t sb = (uint32_t)(g % 3), sp = (uint32_t)((g / 3) & 1);
+      const uint32_t s_addr = lane_addr + sb * 128 + half * 64;
       const int k_len = p.S - bi.j * 128 < 128 ? p.S - bi.j * 128 : 128;
       const int n_mine = k_len - half * 64 >= 64 ? 64 : (k_len - half * 64 > 0 ? k_len - half * 64 : 0);  // 0, 32 or 64
-      if (!(ok = mbar_wait(bar_s_full + 8 * (uint32_t)(g & 1), (uint32_t)((g >> 1) & 1), abort_flag, p.status, 8u))) break;
+      if (!(ok = mbar_wait(bar_s_full + 8 * sb, sp, abort_flag, p.status, 8u))) break;
       tc_fence_after();
       uint32_t v0[32], v1[32];
       if (n_mine >= 32) tmem_ld32(s_addr, v0);
@@ -531,22 +566,24 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (bi.j > 0 && __any_sync(0xffffffffu, grow)) {
         // O holds sum_{i<j} P_i V_i relative to the old offset: wait for P_{j-1} V_{j-1}, then rescale this
         // thread's 32 output columns (rows of the warp that kept their offset multiply by 1)
-        if (!(ok = mbar_wait(bar_pv + 8 * (uint32_t)((g - 1) & 1), (uint32_t)(((g - 1) >> 1) & 1), abort_flag, p.status,
+        if (!(ok = mbar_wait(bar_pv + 8 * (uint32_t)((g - 1) % 3), (uint32_t)(((g - 1) / 3) & 1), abort_flag, p.status,
                              8u)))
           break;
         tc_fence_after();
-        {
+#pragma unroll 1
+        for (int acc = 0; acc < (p.S > 64 ? 2 : 1); ++acc) {
           uint32_t o[32];
-          tmem_ld32(lane_addr + kFlashOCol + half * 32, o);
+          const uint32_t o_addr = lane_addr + (acc ? kOColB : kOColA) + half * 32;
+          tmem_ld32(o_addr, o);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(lane_addr + kFlashOCol + half * 32, o);
+          tmem_st32(o_addr, o);
         }
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar_p_full + 8 * (uint32_t)(g & 1));
+      mbar_arrive(bar_p_full + 8 * sb);
 
       if (bi.j == nb - 1) {
         // ---- the tile's last block: normalise and store once its P V has been accumulated ----
@@ -554,7 +591,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         const float l_tot = l_run + s_red[half ^ 1][row_in_tile];
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        if (!(ok = mbar_wait(bar_pv + 8 * (uint32_t)(g & 1), (uint32_t)((g >> 1) & 1), abort_flag, p.status, 8u))) break;
+        if (!(ok = mbar_wait(bar_pv + 8 * sb, sp, abort_flag, p.status, 8u))) break;
         tc_fence_after();
         const int64_t item = blockIdx.x + (int64_t)bi.it * gridDim.x;
         const int b = (int)(item / p.heads), h = (int)(item % p.heads);
@@ -562,7 +599,14 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const float inv = 1.0f / l_tot;
         float *orow = p.out + (int64_t)b * p.o_batch + (int64_t)row * p.o_row + (int64_t)h * p.o_head + half * 32;
         uint32_t o[32];
-        tmem_ld32(lane_addr + kFlashOCol + half * 32, o);
+        tmem_ld32(lane_addr + kOColA + half * 32, o);
+        if (p.S > 64) {  // accumulator B exists once a block has more than 64 keys
+          uint32_t o2[32];
+          tmem_ld32(lane_addr + kOColB + half * 32, o2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) + __uint_as_float(o2[i]));
+        }
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(bar_o_empty);
@@ -596,6 +640,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     tmem_dealloc(tmem_base, 512);
   }
 }
+
 
 int encode_qkv_map(CUtensorMap *map, const float *base, const b200_attention_desc &d, int64_t row, int64_t head,
                    int64_t batch, CUtensorMapSwizzle swizzle) {
@@ -648,8 +693,8 @@ int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, 
   if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return fail(B200_ECUDA, "attention: cannot set dynamic shared memory to %d", smem);
   const int64_t grid = p.items < kNumSMs ? p.items : kNumSMs;
-  // Rows of up to 384 scores stay resident in TMEM (two-pass softmax, measured 239 against 201 TFLOP/s at S = 384:
-  // the streaming form pays a P V -> rescale -> P V dependency per key block); longer rows stream.
+  // Rows of up to 384 scores stay resident in TMEM (two-pass softmax; measured 264-270 against 249-254 TFLOP/s for
+  // the streaming kernel at S = 384); longer rows stream.
 #ifndef B200_ATTENTION_ALWAYS_STREAM  // build-time switch for comparing the two kernels on sequences both can run
   if (d.seq <= kMaxS)
 #else
@@ -661,7 +706,7 @@ int attention_tc(cudaStream_t st, const b200_attention_desc &d, const float *Q, 
   }
   if (cudaFuncSetAttribute(attention_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return fail(B200_ECUDA, "attention: cannot set dynamic shared memory to %d", smem);
-  attention_stream_kernel<<<(unsigned)grid, kThreads, smem, st>>>(mq, mk, mv, p);
+  attention_stream_kernel<<<(unsigned)grid, kThreads2, smem, st>>>(mq, mk, mv, p);
   return check_launch("attention_stream");
 }
 
