@@ -205,6 +205,8 @@ class BertEncoderB200:
             raise ValueError("out_host must have the input's shape")
         bsz, seq, _ = x_host.shape
         mb = min(self.micro_batch, max(bsz, 1))
+        if 64 <= bsz <= self.micro_batch:
+            mb = (bsz + 1) // 2  # a batch that fits one micro-batch still moves in two, so that copies overlap compute
         buf = self._buffers(mb, seq)
         if self._io is None or self._io[0] != (mb, seq):
             e = lambda: torch.empty(mb, seq, self.hidden, device=self.device, dtype=torch.float32)  # noqa: E731

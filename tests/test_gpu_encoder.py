@@ -62,6 +62,10 @@ def test_host_entry_overlapped_copies_match_device_path(cuda):
         ref = enc.forward_device(x.to(cuda))
         assert torch.equal(y_dev, ref) and torch.equal(y_host, ref.cpu())
     assert torch.equal(enc(x), ref.cpu())  # __call__ without a device copy of the output
+    # a batch that fits one micro-batch (64..micro_batch sequences) is still moved in two halves
+    big = BertEncoderB200(layers, heads=2, device=cuda, micro_batch=128)
+    xb = torch.randn(70, 32, 128, generator=torch.Generator().manual_seed(42)).pin_memory()
+    assert torch.equal(big(xb), big.forward_device(xb.to(cuda)).cpu())
 
 
 def test_rejects_wrong_inputs(cuda):
