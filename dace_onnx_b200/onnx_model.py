@@ -12,7 +12,6 @@ ReduceMean, Add/Sub/Mul/Div/Pow, Sqrt, Erf, Relu, plus MaxPool and Transpose / R
 anything else raises `UnsupportedNode` when the plan is built - there is no other runtime to fall back on,
 and nothing here computes on the CPU.
 """
-import ctypes
 import re
 from typing import Dict, List, Sequence
 
