@@ -207,6 +207,19 @@ class BertEncoderB200:
         mb = min(self.micro_batch, max(bsz, 1))
         if 64 <= bsz <= self.micro_batch:
             mb = (bsz + 1) // 2  # a batch that fits one micro-batch still moves in two, so that copies overlap compute
+        # Only the first host->device and the last device->host copy are not hidden behind compute: a larger batch
+        # starts and ends with a half-size micro-batch.
+        edge = mb // 2 if bsz >= 2 * self.micro_batch and mb >= 64 else 0
+        bounds, b0 = [], 0
+        while b0 < bsz:
+            if edge and b0 == 0:
+                b = edge
+            elif edge and bsz - b0 <= mb + edge and bsz - b0 > edge:
+                b = bsz - b0 - edge
+            else:
+                b = min(mb, bsz - b0)
+            bounds.append((b0, b))
+            b0 += b
         buf = self._buffers(mb, seq)
         if self._io is None or self._io[0] != (mb, seq):
             e = lambda: torch.empty(mb, seq, self.hidden, device=self.device, dtype=torch.float32)  # noqa: E731
@@ -216,8 +229,7 @@ class BertEncoderB200:
         s_in.wait_stream(main)   # staging buffers may still be in use by earlier work on the main stream
         s_out.wait_stream(main)
         ev_in, ev_done, ev_out = [], [], []
-        for i, b0 in enumerate(range(0, bsz, mb)):
-            b = min(mb, bsz - b0)
+        for i, (b0, b) in enumerate(bounds):
             slot = i % 2
             with torch.cuda.stream(s_in):
                 if i >= 2:

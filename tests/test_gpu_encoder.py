@@ -66,6 +66,10 @@ def test_host_entry_overlapped_copies_match_device_path(cuda):
     big = BertEncoderB200(layers, heads=2, device=cuda, micro_batch=128)
     xb = torch.randn(70, 32, 128, generator=torch.Generator().manual_seed(42)).pin_memory()
     assert torch.equal(big(xb), big.forward_device(xb.to(cuda)).cpu())
+    # two or more micro-batches of at least 64: the schedule starts and ends with a half-size one (32, 64, 22, 32)
+    mid = BertEncoderB200(layers, heads=2, device=cuda, micro_batch=64)
+    xm = torch.randn(150, 32, 128, generator=torch.Generator().manual_seed(43)).pin_memory()
+    assert torch.equal(mid(xm), mid.forward_device(xm.to(cuda)).cpu())
 
 
 def test_rejects_wrong_inputs(cuda):
