@@ -12,12 +12,19 @@ uses all host threads the way DaCe's OpenMP maps do). Citations are paths inside
 
 How it is pinned. The reference holds no golden vectors: its tests compare each expansion with
 torch / numpy on unseeded random inputs (tests/pure_expansions/test_expansions.py,
-test_conv_expansion.py, tests/pytorch/test_bert_encoder.py). The reference itself cannot be
-imported where this repository is developed (dace, onnx missing; Python 3.12 vs the pinned <3.10),
-so the oracle is pinned the way the reference pins itself: `tests/test_oracle_pins.py` repeats
-those tests' shapes, comparators and tolerances against this module, and `tests/golden/` holds
-seeded input/output vectors produced by it. Against outputs of the reference *executed* here the
-parity is unpinned.
+test_conv_expansion.py, tests/pytorch/test_bert_encoder.py), and DaCe cannot be installed where
+this repository is developed (dace, onnx missing; Python 3.12 vs the pinned <3.10). Two pins:
+  1. `tests/golden/ref_pins.npz` holds vectors computed by the reference's OWN source:
+     `tests/golden/make_reference_pins.py` loads pure_implementations.py and
+     op_implementations/utils.py unmodified, calls each Pure<Op>.forward() and executes the numpy-style
+     program it hands to DaCe with numpy arrays (MatMul: the einsum string it builds, through
+     np.einsum). `tests/test_reference_pins.py` holds this module to those vectors -- elementwise
+     nodes bit for bit, reductions / contractions within 2e-6 -- for every node on the path and for
+     the LayerNorm, Gelu and attention node chains. Not covered by this pin: DaCe's code generation
+     (loop order, libm), and Conv, whose expansion is written in DaCe map / tasklet syntax.
+  2. `tests/test_oracle_pins.py` repeats the reference tests' shapes, comparators and tolerances
+     (torch / numpy as the yardstick) against this module, Conv included.
+Against outputs of the DaCe-compiled reference the parity remains unpinned.
 """
 import math
 
