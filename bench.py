@@ -29,6 +29,12 @@ WORKLOADS = {
     "bert_base_x1_b64_s512_tf32": (1, 768, 12, 3072, 64, 512, "tf32"),
 }
 DEFAULT_WORKLOAD = "bert_large_x24_b1024_s384_tf32"
+# DRAM bytes (read + write) per launch from the committed ncu summaries, with the algorithmic bytes of the captured
+# launch: the roofline's `traffic` scales these to the bench's launch size.
+NCU_TRAFFIC = {
+    "gemm_tc_pair_kernel": {"profile": "profiles/gemm_tc_pair_tf32_qkv_16384x3072x1024.txt",
+                            "dram_bytes": 232.7e6, "algorithmic_bytes": 281.0e6},
+}
 METRIC = "bert_encoder_seqs_per_s"
 UNIT = "seqs/s"
 
@@ -158,25 +164,38 @@ def run_b200(args, wl):
     params = [synthetic_layer_params(hidden, ffn, seed=100 + i) for i in range(layers)]
     enc = BertEncoderB200(params, heads, device=device, math_mode=mode, micro_batch=args.micro_batch)
     del params
-    lo, hi = sharding.shard_bounds(batch, world, rank)
-    local = hi - lo
+    if batch % world:
+        raise SystemExit("the batch (%d) must divide among %d ranks" % (batch, world))
+    local = batch // world
     x_host = torch.randn(local, seq, hidden, generator=torch.Generator().manual_seed(7 + rank)).pin_memory()
     y_host = torch.empty(local, seq, hidden).pin_memory()
     x_dev = x_host.to(device)
     y_local = torch.empty_like(x_dev)
     y_full = torch.empty(batch, seq, hidden, device=device) if world > 1 else None
+    # The outputs are all-gathered piece by piece while later pieces still compute (sharding.OverlappedGather):
+    # one piece per micro-batch, the last micro-batch's final layer cut into `--tail-chunks` pieces.
+    gather_events = []
+    tail = args.tail_chunks if world > 1 else 1
+    g_dev = sharding.OverlappedGather(batch, enc.device_chunks(local, tail), timeline=gather_events)
+    g_host = sharding.OverlappedGather(batch, enc.host_chunks(local), timeline=gather_events)
 
     def step_device():
-        enc.forward_device(x_dev, out=y_local)
         if world > 1:
-            sharding.all_gather_batch(y_local, batch, out=y_full)
+            enc.forward_device(x_dev, out=y_local, tail_chunks=tail,
+                               on_chunk=lambda lo, n: g_dev.chunk_done(y_local, y_full, lo, n))
+            g_dev.finish(device)
+        else:
+            enc.forward_device(x_dev, out=y_local)
 
     def step_e2e():
         # pinned host input -> device -> layers -> pinned host output, micro-batch copies overlapped
         # with compute; the local result also stays on the device for the all-gather
-        enc.forward_host(x_host, y_host, out_device=y_local)
         if world > 1:
-            sharding.all_gather_batch(y_local, batch, out=y_full)
+            enc.forward_host(x_host, y_host, out_device=y_local,
+                             on_chunk=lambda lo, n: g_host.chunk_done(y_local, y_full, lo, n))
+            g_host.finish(device)
+        else:
+            enc.forward_host(x_host, y_host, out_device=y_local)
 
     def barrier():
         if world > 1:
@@ -201,10 +220,12 @@ def run_b200(args, wl):
     sampler = ClockSampler(local_rank)
     sampler.start()
     enc.timeline = []
+    del gather_events[:]
     launches0 = enc.launches
     ms_step = timed(step_device, args.steps)
     launches = enc.launches - launches0
     timeline, enc.timeline = enc.timeline, None
+    gathers = list(gather_events)
     clocks = sampler.stop()
     for _ in range(min(args.warmup, 1)):
         step_e2e()
@@ -234,21 +255,31 @@ def run_b200(args, wl):
     total_sec = sum(v[0] for v in per_kind.values()) or 1.0
     for kind in ops_report:
         ops_report[kind]["share"] = per_kind[kind][0] / total_sec
+    if gathers:
+        # the output all-gather, timed with its own events on the side stream it runs on; it overlaps the kernels
+        # above except for its last piece, so it has no share of the kernel time
+        g_sec = sum(a.elapsed_time(b) for a, b, _ in gathers) * 1e-3
+        g_bytes = sum(n for _, _, n in gathers)
+        last_ms = gathers[-1][0].elapsed_time(gathers[-1][1])
+        ops_report["allgather"] = {"launches": len(gathers), "ms_per_step": g_sec * 1e3 / args.steps, "share": None,
+                                   "gbs": g_bytes / g_sec / 1e9 if g_sec else None, "pieces_per_step": len(gathers) // args.steps,
+                                   "last_piece_ms": last_ms,
+                                   "note": "runs on a side stream under the next piece's kernels; only the last piece is exposed"}
     g = per_kind.get("gemm", [1.0, 0.0, 0.0, 1])
-    # DRAM traffic of the dense GEMM kernel: ncu measured dram read+write = 0.83 x the algorithmic bytes
-    # 4(MK+NK+MN) on the captured small case (profiles/gemm_tc_tf32_qkv_16384x3072x1024.txt: 232.7 MB vs
-    # 281.0 MB; part of the output is still in L2 when the kernel ends). Traffic grows in proportion to M,
-    # so the per-launch figure here is that ratio times the average algorithmic bytes of a bench launch.
-    t_tok = min(args.micro_batch, local) * seq
+    # DRAM traffic of the dense GEMM kernel: dram__bytes_read + dram__bytes_write of one ncu capture of a smaller
+    # launch (NCU_TRAFFIC below names the summary file), scaled by the algorithmic bytes 4(MK+NK+MN): traffic grows
+    # in proportion to M. The per-launch figure is that ratio times the average algorithmic bytes of a bench launch.
+    t_tok = min(enc.micro_batch, local) * seq
     gemm_shapes = [(3 * hidden, hidden), (hidden, hidden), (ffn, hidden), (hidden, ffn)]
     alg_bytes = sum(4 * (t_tok * k + n * k + t_tok * n) for n, k in gemm_shapes) / len(gemm_shapes)
-    traffic = 0.83 * alg_bytes
+    cap = NCU_TRAFFIC["gemm_tc_pair_kernel"]
+    traffic = cap["dram_bytes"] / cap["algorithmic_bytes"] * alg_bytes
     achieved = g[1] / g[0] / 1e12
     roofline = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<256, K-major> (TF32 dense projections, CTA pairs)",
                 "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                 "peak_source": "%s bf16 sustained / 2 (TF32 runs at half the bf16 rate)" % peaks["source"],
                 "avg_launch_ms": g[0] * 1e3 / max(g[3], 1), "traffic": traffic,
-                "traffic_unit": "bytes per launch (scaled from an ncu capture of a smaller launch)",
+                "traffic_unit": "bytes per launch (scaled from the ncu capture in %s)" % cap["profile"],
                 "algorithmic_bytes": alg_bytes}
 
     line = None
@@ -259,18 +290,25 @@ def run_b200(args, wl):
         else:
             cpu_baseline = None
         bytes_io = local * seq * hidden * 4
+        per_config = None
+        if world == 1 and not args.no_per_config:
+            del x_dev, y_local
+            enc.release_buffers()
+            torch.cuda.empty_cache()
+            per_config = per_config_report(device, peaks)
         line = {
             "metric": METRIC, "value": batch / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "tf32" if mode == "tf32" else "f32", "data": "synthetic",
             "config": {"workload": wl, "layers": layers, "hidden": hidden, "heads": heads, "ffn": ffn,
                        "global_batch": batch, "seq_len": seq, "parallelism": "batch-sharded x%d, output all-gather" % world,
-                       "math_mode": mode, "micro_batch": enc.micro_batch,
+                       "math_mode": mode, "micro_batch": min(enc.micro_batch, local),
+                       "gather_pieces": len(g_dev.chunks) if world > 1 else 0,
                        "l2": "inputs larger than L2 (every activation tensor of a micro-batch exceeds 126 MB)"},
             "e2e": {"value": batch / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": bytes_io,
                     "d2h_bytes_per_step": bytes_io, "ms_per_step": ms_e2e},
             "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu_baseline,
-            "ops": ops_report,
+            "ops": ops_report, "per_config": per_config,
             "tflops_algorithmic": enc.flops_per_sequence(seq) * batch / (ms_step * 1e-3) / 1e12 / world,
         }
     if world > 1:
@@ -368,16 +406,76 @@ def kernel_cases(device):
             return fn, 4 * b * h * s * s * d, 16 * b * s * h * d, "tensor"
         return make
 
+    def conv_inputs(n, c, hw, m):
+        x = torch.rand(n, c, hw, hw, device=device, generator=g)
+        bound = 1.0 / (c * 9) ** 0.5
+        w = (torch.rand(m, c, 3, 3, device=device, generator=g) * 2 - 1) * bound
+        b = (torch.rand(m, device=device, generator=g) * 2 - 1) * bound
+        return x, w, b
+
     def conv(n, c, hw, m, mode):
+        # the one-call entry (b200_conv2d_f32): filter repack + NCHW -> NHWC + kernel, NCHW out
         def make():
-            x = torch.rand(n, c, hw, hw, device=device, generator=g)
-            bound = 1.0 / (c * 9) ** 0.5
-            w = (torch.rand(m, c, 3, 3, device=device, generator=g) * 2 - 1) * bound
-            b = (torch.rand(m, device=device, generator=g) * 2 - 1) * bound
+            x, w, b = conv_inputs(n, c, hw, m)
             y = torch.empty(n, m, hw, hw, device=device)
             ws = torch.empty(2 * x.numel() * 4 + (1 << 20), device=device, dtype=torch.uint8)
             fn = lambda: ops.conv2d(x, w, b, out=y, pads=(1, 1, 1, 1), relu=True, workspace=ws, math_mode=mode)  # noqa
             return fn, 2 * n * hw * hw * m * c * 9, 4 * (x.numel() + y.numel()), "tensor"
+        return make
+
+    def conv_nhwc(n, c, hw, m, mode):
+        # the convolution kernel alone: prepared filter, NHWC in and out (a layer inside a stack)
+        def make():
+            x, w, b = conv_inputs(n, c, hw, m)
+            xn = x.permute(0, 2, 3, 1).contiguous()
+            cv = ops.PreparedConv(w, b, pads=(1, 1, 1, 1), relu=True, math_mode=mode)
+            y = torch.empty(n, hw, hw, m, device=device)
+            fn = lambda: cv(xn, out=y, x_nhwc=True, y_nhwc=True)  # noqa: E731
+            return fn, 2 * n * hw * hw * m * c * 9, 4 * (x.numel() + y.numel()), "tensor"
+        return make
+
+    def conv_stack(n, c, hw, layers, mode):
+        # configuration 2: `layers` convolutions, NCHW in, NCHW out, NHWC in between, filters prepared once
+        def make():
+            from dace_onnx_b200 import graphs
+            x = torch.rand(n, c, hw, hw, device=device, generator=g)
+            params = [conv_inputs(1, c, 4, c)[1:] for _ in range(layers)]
+            prepared = graphs.prepare_conv_stack(params, math_mode=mode)
+            ws = torch.empty(x.numel() * 4 + 256, device=device, dtype=torch.uint8)
+            fn = lambda: graphs.conv_stack_forward(x, prepared, workspace=ws)  # noqa: E731
+            return fn, layers * 2 * n * hw * hw * c * c * 9, layers * 8 * x.numel(), "tensor"
+        return make
+
+    def binary(shape_a, shape_b, op):
+        def make():
+            a, b = rn(*shape_a), rn(*shape_b)
+            out = torch.empty(torch.broadcast_shapes(a.shape, b.shape), device=device)
+            fn = lambda: getattr(ops, op)(a, b, out=out)  # noqa: E731
+            return fn, 0, 4 * (a.numel() + b.numel() + out.numel()), "hbm"
+        return make
+
+    def unary(op, n):
+        def make():
+            x = rn(n)
+            y = torch.empty_like(x)
+            return (lambda: getattr(ops, op)(x, out=y)), 0, 8 * n, "hbm"
+        return make
+
+    def rowwise(op, rows, length):
+        def make():
+            x = rn(rows, length, std=2.0)
+            if op == "reduce_mean":
+                y = torch.empty(rows, 1, device=device)
+                return (lambda: ops.reduce_mean(x, [-1], 1, out=y)), 0, 4 * x.numel() + 4 * rows, "hbm"
+            y = torch.empty_like(x)
+            return (lambda: getattr(ops, op)(x, -1, out=y)), 0, 8 * x.numel(), "hbm"
+        return make
+
+    def transpose(batch, rows, cols):
+        def make():
+            x = rn(batch, rows, cols)
+            y = torch.empty(batch, cols, rows, device=device)
+            return (lambda: ops.transpose_last2(x, out=y)), 0, 8 * x.numel(), "hbm"
         return make
 
     def frontdoor_bert_layer(b, s, hidden, heads, ffn, mode):
@@ -430,7 +528,18 @@ def kernel_cases(device):
         "frontdoor_mlp_c1": frontdoor_mlp_c1(), "frontdoor_mlp_c1_cudagraph": frontdoor_mlp_c1(True),
         "frontdoor_mlp_c1_cudagraph_fp32": frontdoor_mlp_c1(True, "fp32"),
         "frontdoor_mlp_c1_cudagraph_tf32": frontdoor_mlp_c1(True, "tf32"),
+        "encoder_bert_base_layer_fp32x3": encoder_bert_layer(64, 512, 768, 12, 3072, "fp32x3"),
+        "encoder_bert_base_layer_tf32": encoder_bert_layer(64, 512, 768, 12, 3072, "tf32"),
         "conv_c2_fp32x3": conv(256, 64, 56, 64, "fp32x3"), "conv_c2_tf32": conv(256, 64, 56, 64, "tf32"),
+        "conv_c2_nhwc_fp32x3": conv_nhwc(256, 64, 56, 64, "fp32x3"), "conv_c2_nhwc_tf32": conv_nhwc(256, 64, 56, 64, "tf32"),
+        "conv_c2_stack_fp32x3": conv_stack(256, 64, 56, 2, "fp32x3"), "conv_c2_stack_tf32": conv_stack(256, 64, 56, 2, "tf32"),
+        "conv_nhwc_small_tf32": conv_nhwc(64, 64, 56, 64, "tf32"), "conv_nhwc_small_fp32x3": conv_nhwc(64, 64, 56, 64, "fp32x3"),
+        "add_full": binary((32768, 1024), (32768, 1024), "add"), "add_row_bias": binary((32768, 1024), (1024,), "add"),
+        "mul_scalar": binary((32768, 1024), (1,), "mul"), "erf": unary("erf", 32768 * 1024), "gelu": unary("gelu", 32768 * 1024),
+        "relu": unary("relu", 32768 * 1024), "logsoftmax_rows512": rowwise("logsoftmax", 131072, 512),
+        "reduce_mean_65536x1024": rowwise("reduce_mean", 65536, 1024),
+        "transpose_nchw_to_nhwc_64x64x3136": transpose(64, 64, 3136),
+        "attention_fused_tf32_b256": attn_fused(256, 16, 384, 64),
         "softmax_c4": softmax_c4, "layernorm_c4": layernorm_c4,
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),
         "gemm_tf32_ffn2": gemm(16384, 1024, 4096, "tf32"), "gemm_tf32_proj": gemm(16384, 1024, 1024, "tf32"),
@@ -443,53 +552,101 @@ def kernel_cases(device):
     }
 
 
+def time_case(make, steps, warmup, reps=3):
+    """Median over `reps` brackets of the mean launch time inside ONE event pair around `steps` back-to-back
+    launches (host launch latency stays outside the GPU's critical path once the queue is primed). The launches
+    rotate over independent buffer sets totalling more than 256 MB, so no launch finds its operands in the 126 MB
+    L2; nothing else runs inside the bracket. Follows the reference's convention of warm-ups and many iterations
+    between one pair of events (daceml/testing/profiling/event_profiler.py:87-120).
+    Returns (ms, flops, bytes, bound, sets)."""
+    first = make()
+    sets = [first]
+    total = first[2]
+    while first[2] and total < 256e6 and len(sets) < 32:
+        sets.append(make())
+        total += first[2]
+    fns = [c[0] for c in sets]
+    for i in range(max(warmup, len(fns))):
+        fns[i % len(fns)]()
+    torch.cuda.synchronize()
+    brackets = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fns[i % len(fns)]()
+        e1.record()
+        torch.cuda.synchronize()
+        brackets.append(e0.elapsed_time(e1) / steps)
+    return sorted(brackets)[len(brackets) // 2], first[1], first[2], first[3], len(sets)
+
+
+def per_config_report(device, peaks):
+    """The other BASELINE configurations, a few seconds in total: C1 MLP (one CUDA-graph replay), C2 convolution
+    stack per layer in both tensor-core modes, C3 BERT-base layer in the fp32-accurate mode, C4 bandwidth cases."""
+    cases = kernel_cases(device)
+    out = {}
+
+    def run(name, steps=20, warmup=5):
+        ms, flops, nbytes, bound, _ = time_case(cases[name], steps, warmup)
+        torch.cuda.empty_cache()
+        return ms, flops, nbytes
+
+    ms, flops, nbytes = run("frontdoor_mlp_c1_cudagraph", steps=100)
+    out["c1_mlp_b4096_fp32x3"] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    for mode in ("fp32x3", "tf32"):
+        ms, flops, nbytes = run("conv_c2_stack_" + mode)
+        out["c2_conv_stack_b256_" + mode] = {"ms_per_layer": ms / 2, "tflops": flops / ms / 1e9,
+                                             "frac_tf32_burst": flops / ms / 1e9 / (peaks["bf16"] / 2)}
+    ms, flops, nbytes = run("encoder_bert_base_layer_fp32x3", steps=10, warmup=3)
+    out["c3_bert_base_layer_b64_s512_fp32x3"] = {"seqs_per_s": 64 / (ms * 1e-3), "ms": ms, "tflops": flops / ms / 1e9}
+    for name, key in (("softmax_c4", "c4_softmax_768x512x512"), ("layernorm_c4", "c4_layernorm_65536x1024")):
+        ms, flops, nbytes = run(name)
+        out[key] = {"us": ms * 1e3, "gbs": nbytes / ms / 1e6, "frac_hbm": nbytes / ms / 1e6 / peaks["hbm_gbs"]}
+    return out
+
+
 def run_kernel_case(args):
     from dace_onnx_b200 import _lib
     device = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     cases = kernel_cases(device)
-    names = sorted(cases) if args.kernel == "all" else [args.kernel]
+    names = sorted(cases) if args.kernel == "all" else args.kernel.split(",")
     peaks = measured_peaks()
-    flush = torch.empty(64 * 1024 * 1024, device=device)  # 256 MB > L2, rewritten between iterations
     for name in names:
-        fn, flops, nbytes, bound = cases[name]()
-        for _ in range(args.warmup):
-            fn()
-        times = []
-        for _ in range(args.steps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
+        ms, flops, nbytes, bound, nsets = time_case(cases[name], args.steps, args.warmup)
         _lib.device_status()
-        ms = sorted(times)[len(times) // 2]
         if bound == "tensor":
             peak = peaks["bf16"] / 2.0  # a kernel timed alone: burst figure
             achieved, unit = flops / (ms * 1e-3) / 1e12, "TFLOP/s"
         else:
             peak, achieved, unit = peaks["hbm_gbs"], nbytes / (ms * 1e-3) / 1e9, "GB/s"
         print(json.dumps({"kernel_case": name, "ms": ms, "steps": args.steps, "warmup": args.warmup,
-                          "l2": "flushed (256 MB memset) before every timed launch",
+                          "l2": "%d independent buffer sets in rotation (operands exceed L2), %d back-to-back "
+                                "launches per event pair" % (nsets, args.steps),
                           "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                                        "frac": achieved / peak, "peak_source": peaks["source"]},
                           "tflops": flops / (ms * 1e-3) / 1e12 if flops else None,
                           "gbs": nbytes / (ms * 1e-3) / 1e9}), flush=True)
+        torch.cuda.empty_cache()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default=None, help="run one single-kernel case (or 'all') instead of the encoder")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 5; 20 launches for --kernel)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--micro-batch", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (configs 1-4)")
+    ap.add_argument("--tail-chunks", type=int, default=4,
+                    help="pieces the last micro-batch's final layer is cut into for the overlapped all-gather")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 20 if args.kernel else 5
     if args.kernel:
         run_kernel_case(args)
     elif args.impl == "reference":

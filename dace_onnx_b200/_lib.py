@@ -14,6 +14,7 @@ MATH_FP32X3, MATH_TF32, MATH_FP32 = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_SCALE = range(6)
 ADD, SUB, MUL, DIV, POW = range(5)
 SQRT, ERF, RELU, GELU = range(4)
+CONV_X_NHWC, CONV_Y_NHWC = 1, 2
 
 MATH_MODES = {"fp32x3": MATH_FP32X3, "tf32": MATH_TF32, "fp32": MATH_FP32}
 
@@ -60,6 +61,12 @@ SIGNATURES = {
     "b200_conv2d_workspace_bytes": (c_size_t, [POINTER(ConvDesc)]),
     "b200_conv2d_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_size_t]),
+    "b200_conv2d_filter_bytes": (c_size_t, [POINTER(ConvDesc)]),
+    "b200_conv2d_prepare_filter_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_size_t]),
+    "b200_conv2d_nhwc_supported": (c_int, [POINTER(ConvDesc)]),
+    "b200_conv2d_prepared_workspace_bytes": (c_size_t, [POINTER(ConvDesc), c_int]),
+    "b200_conv2d_prepared_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_size_t]),
     "b200_conv2d_static_scratch_bytes": (c_size_t, []),
     "b200_conv2d_static_f32": (c_int, [c_void_p, POINTER(ConvDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_softmax_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),

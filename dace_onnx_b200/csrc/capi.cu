@@ -141,7 +141,7 @@ extern "C" B200_API int b200_attention_f32(void *stream, const b200_attention_de
   if (!Q || !K || !V || !out) return fail(B200_EINVAL, "attention: null pointer");
   if (!b200_attention_supported(desc, Q, K, V, out))
     return fail(B200_EUNSUPPORTED,
-                "attention: fused kernel needs TF32 mode, head_dim 64, seq %% 32 == 0 and <= 384, aligned strides "
+                "attention: fused kernel needs TF32 mode, head_dim 64, seq %% 32 == 0, aligned strides "
                 "(got mode %d, head_dim %lld, seq %lld); run the unfused nodes instead",
                 desc->math_mode, (long long)desc->head_dim, (long long)desc->seq);
   return attention_tc((cudaStream_t)stream, *desc, Q, K, V, out);
@@ -156,11 +156,33 @@ static bool conv_out_shape(const b200_conv_desc &d, int64_t *oh, int64_t *ow) {
   return true;
 }
 
+namespace {
+inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// Argument checks shared by the convolution entry points; on success *bias is null unless the epilogue uses it.
+int conv_check(const char *who, const b200_conv_desc &d, const float *X, const void *W, const float **bias,
+               const float *Y, int64_t *OH, int64_t *OW, bool *empty) {
+  if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.M < 0) return fail(B200_EINVAL, "%s: bad extent", who);
+  if (!conv_out_shape(d, OH, OW)) return fail(B200_EINVAL, "%s: bad kernel/pad/stride", who);
+  *empty = d.N == 0 || d.M == 0;
+  if (*empty) return B200_OK;
+  if (!X || !W || !Y) return fail(B200_EINVAL, "%s: null pointer", who);
+  if (d.epilogue != B200_EPI_NONE && d.epilogue != B200_EPI_BIAS && d.epilogue != B200_EPI_BIAS_RELU)
+    return fail(B200_EINVAL, "%s: unsupported epilogue %d", who, d.epilogue);
+  if (d.epilogue != B200_EPI_NONE && !*bias) return fail(B200_EINVAL, "%s: epilogue %d needs a bias", who, d.epilogue);
+  if (d.epilogue == B200_EPI_NONE) *bias = nullptr;
+  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
+    return fail(B200_EINVAL, "%s: unknown math mode %d", who, d.math_mode);
+  return B200_OK;
+}
+}  // namespace
+
+// b200_conv2d_f32 = prepare + run on the caller's workspace: [NHWC copy of X | prepared filter]
 extern "C" B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc) {
   if (!desc) return 0;
   // alignment of X is unknown here; the tensor-core path needs this much whenever the shape allows it
-  static const float *const kAligned = nullptr;
-  return conv2d_tc_supported(*desc, kAligned) ? conv2d_tc_workspace_bytes(*desc) : 0;
+  if (!conv2d_tc_supported(*desc, nullptr)) return 0;
+  return up256(conv2d_run_workspace_bytes(*desc, 0)) + conv2d_filter_bytes(*desc);
 }
 
 extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
@@ -168,19 +190,56 @@ extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc
   cudaStream_t st = (cudaStream_t)stream;
   if (!desc) return fail(B200_EINVAL, "conv: null descriptor");
   b200_conv_desc d = *desc;
-  if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.M < 0) return fail(B200_EINVAL, "conv: bad extent");
   int64_t OH, OW;
-  if (!conv_out_shape(d, &OH, &OW)) return fail(B200_EINVAL, "conv: bad kernel/pad/stride");
-  if (d.N == 0 || d.M == 0) return B200_OK;
-  if (!X || !W || !Y) return fail(B200_EINVAL, "conv: null pointer");
-  if (d.epilogue != B200_EPI_NONE && d.epilogue != B200_EPI_BIAS && d.epilogue != B200_EPI_BIAS_RELU)
-    return fail(B200_EINVAL, "conv: unsupported epilogue %d", d.epilogue);
-  if (d.epilogue != B200_EPI_NONE && !bias) return fail(B200_EINVAL, "conv: epilogue %d needs a bias", d.epilogue);
-  if (d.epilogue == B200_EPI_NONE) bias = nullptr;
-  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
-    return fail(B200_EINVAL, "conv: unknown math mode %d", d.math_mode);
+  bool empty;
+  if (int rc = conv_check("conv", d, X, W, &bias, Y, &OH, &OW, &empty)) return rc;
+  if (empty) return B200_OK;
   // Tensor-core implicit GEMM when TMA can address the NHWC copy; the CUDA-core kernel otherwise
   // (strided convolutions, channel counts that are not multiples of 4, plain fp32 arithmetic).
-  if (conv2d_tc_supported(d, X)) return conv2d_tc(st, d, X, W, bias, Y, OH, OW, workspace, workspace_bytes);
-  return conv2d_simt(st, d, X, W, bias, Y, OH, OW);
+  if (!conv2d_tc_supported(d, X)) return conv2d_simt(st, d, X, W, bias, Y, OH, OW);
+  const size_t xt_bytes = up256(conv2d_run_workspace_bytes(d, 0)), f_bytes = conv2d_filter_bytes(d);
+  if (!workspace || workspace_bytes < xt_bytes + f_bytes)
+    return fail(B200_EWORKSPACE, "conv: workspace of %zu bytes needed, %zu given", xt_bytes + f_bytes, workspace_bytes);
+  if (!aligned16(workspace)) return fail(B200_EINVAL, "conv: workspace must be 16-byte aligned");
+  void *filter = static_cast<char *>(workspace) + xt_bytes;
+  if (int rc = conv2d_prepare_filter(st, d, W, filter, f_bytes)) return rc;
+  return conv2d_run(st, d, 0, X, filter, bias, Y, OH, OW, workspace, xt_bytes);
+}
+
+extern "C" B200_API size_t b200_conv2d_filter_bytes(const b200_conv_desc *desc) {
+  if (!desc || desc->M < 1 || desc->C < 1 || desc->KH < 1 || desc->KW < 1) return 0;
+  return conv2d_filter_bytes(*desc);
+}
+
+extern "C" B200_API int b200_conv2d_prepare_filter_f32(void *stream, const b200_conv_desc *desc, const float *W,
+                                                       void *filter, size_t filter_bytes) {
+  if (!desc) return fail(B200_EINVAL, "conv(prepare): null descriptor");
+  if (desc->C < 1 || desc->M < 0 || desc->KH < 1 || desc->KW < 1) return fail(B200_EINVAL, "conv(prepare): bad extent");
+  if (desc->M == 0) return B200_OK;
+  if (!W) return fail(B200_EINVAL, "conv(prepare): null pointer");
+  if (desc->math_mode != B200_MATH_FP32X3 && desc->math_mode != B200_MATH_TF32 && desc->math_mode != B200_MATH_FP32)
+    return fail(B200_EINVAL, "conv(prepare): unknown math mode %d", desc->math_mode);
+  return conv2d_prepare_filter((cudaStream_t)stream, *desc, W, filter, filter_bytes);
+}
+
+extern "C" B200_API int b200_conv2d_nhwc_supported(const b200_conv_desc *desc) {
+  return desc && desc->C >= 1 && desc->M >= 1 && desc->KH >= 1 && desc->KW >= 1 && conv2d_nhwc_supported(*desc) ? 1 : 0;
+}
+
+extern "C" B200_API size_t b200_conv2d_prepared_workspace_bytes(const b200_conv_desc *desc, int flags) {
+  if (!desc || desc->N < 1 || desc->C < 1 || desc->H < 1 || desc->W < 1) return 0;
+  return conv2d_run_workspace_bytes(*desc, flags);
+}
+
+extern "C" B200_API int b200_conv2d_prepared_f32(void *stream, const b200_conv_desc *desc, int flags, const float *X,
+                                                 const void *filter, const float *bias, float *Y, void *workspace,
+                                                 size_t workspace_bytes) {
+  if (!desc) return fail(B200_EINVAL, "conv(prepared): null descriptor");
+  if (flags & ~(B200_CONV_X_NHWC | B200_CONV_Y_NHWC)) return fail(B200_EINVAL, "conv(prepared): unknown flags 0x%x", flags);
+  b200_conv_desc d = *desc;
+  int64_t OH, OW;
+  bool empty;
+  if (int rc = conv_check("conv(prepared)", d, X, filter, &bias, Y, &OH, &OW, &empty)) return rc;
+  if (empty) return B200_OK;
+  return conv2d_run((cudaStream_t)stream, d, flags, X, filter, bias, Y, OH, OW, workspace, workspace_bytes);
 }

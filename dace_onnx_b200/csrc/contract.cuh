@@ -48,12 +48,21 @@ size_t gemm_tc_workspace_bytes(const b200_gemm_desc &d);
 int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
             const float *residual, float *Y, void *workspace = nullptr, size_t workspace_bytes = 0);
 
-// Tensor-core convolution: NCHW -> NHWC and filter repack into the caller's workspace, then the
-// implicit GEMM. Supported for stride 1 and channel counts that are multiples of 4 (>= 16).
+// Tensor-core convolution (stride 1, channel counts that are multiples of 4 and >= 16, 16-byte aligned X).
+// The filter is prepared once (repacked to [M][tap][Cp]; in 3xTF32 mode also split into hi / lo) into
+// conv2d_filter_bytes(d) bytes; conv2d_run then takes NCHW or NHWC tensors (flags B200_CONV_X_NHWC /
+// B200_CONV_Y_NHWC; NHWC only where conv2d_nhwc_supported) and needs conv2d_run_workspace_bytes(d, flags)
+// bytes of scratch (the NHWC copy of an NCHW input). Shapes the tensor cores cannot take run on conv2d_simt.
 bool conv2d_tc_supported(const b200_conv_desc &d, const float *X);
-size_t conv2d_tc_workspace_bytes(const b200_conv_desc &d);
-int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias, float *Y,
-              int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes);
+size_t conv2d_filter_bytes(const b200_conv_desc &d);
+int conv2d_prepare_filter(cudaStream_t st, const b200_conv_desc &d, const float *W, void *filter, size_t filter_bytes);
+bool conv2d_nhwc_supported(const b200_conv_desc &d);
+size_t conv2d_run_workspace_bytes(const b200_conv_desc &d, int flags);
+int conv2d_run(cudaStream_t st, const b200_conv_desc &d, int flags, const float *X, const void *filter,
+               const float *bias, float *Y, int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes);
+// the general implicit-GEMM kernel (any output-channel count; NHWC copy in, NCHW out)
+int conv2d_tc_gemm(cudaStream_t st, const b200_conv_desc &d, const float *xt, const float *wt, const float *bias,
+                   float *Y, int64_t OH, int64_t OW);
 
 bool attention_tc_supported(const b200_attention_desc &d, const float *Q, const float *K, const float *V,
                             const float *out);

@@ -80,7 +80,9 @@ extern "C" B200_API int b200_conv2d_static_f32(void *stream, const b200_conv_des
   // Shapes the tensor cores cannot take run on the CUDA-core kernel, which uses no scratch at all.
   if (!conv2d_tc_supported(d, X)) return conv2d_simt(st, d, X, W, bias, Y, OH, OW);
 
-  const size_t need = conv2d_tc_workspace_bytes(d);
+  // scratch layout as in b200_conv2d_f32: [NHWC copy of X | prepared filter]
+  const size_t xt_bytes = (conv2d_run_workspace_bytes(d, 0) + 255) & ~(size_t)255, f_bytes = conv2d_filter_bytes(d);
+  const size_t need = xt_bytes + f_bytes;
   if (need > (size_t)B200_CONV_STATIC_SCRATCH_BYTES)
     return fail(B200_EWORKSPACE,
                 "conv(static): this convolution needs %zu bytes of scratch, the built-in array holds %zu; "
@@ -88,5 +90,7 @@ extern "C" B200_API int b200_conv2d_static_f32(void *stream, const b200_conv_des
                 need, (size_t)B200_CONV_STATIC_SCRATCH_BYTES);
   void *scratch = nullptr;
   if (int rc = scratch_for_current_device(&scratch)) return rc;
-  return conv2d_tc(st, d, X, W, bias, Y, OH, OW, scratch, (size_t)B200_CONV_STATIC_SCRATCH_BYTES);
+  void *filter = static_cast<char *>(scratch) + xt_bytes;
+  if (int rc = conv2d_prepare_filter(st, d, W, filter, f_bytes)) return rc;
+  return conv2d_run(st, d, 0, X, filter, bias, Y, OH, OW, scratch, xt_bytes);
 }

@@ -123,42 +123,48 @@ transpose_0213_kernel(const float *__restrict__ x, float *__restrict__ y, int64_
 }
 
 __global__ void __launch_bounds__(256)
-transpose_2d_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int64_t cols) {
+transpose_2d_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t batch, int64_t rows, int64_t cols) {
   __shared__ float tile[32][33];
-  const float *xb = x + (int64_t)blockIdx.z * rows * cols;
-  float *yb = y + (int64_t)blockIdx.z * rows * cols;
   const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-  for (int k = ty; k < 32; k += 8)
-    if (r0 + k < rows && c0 + tx < cols) tile[k][tx] = xb[(r0 + k) * cols + c0 + tx];
-  __syncthreads();
-  for (int k = ty; k < 32; k += 8)
-    if (c0 + k < cols && r0 + tx < rows) yb[(c0 + k) * rows + r0 + tx] = tile[tx][k];
+  for (int64_t b = blockIdx.z; b < batch; b += gridDim.z) {  // grid.z is capped at 65535
+    const float *xb = x + b * rows * cols;
+    float *yb = y + b * rows * cols;
+    for (int k = ty; k < 32; k += 8)
+      if (r0 + k < rows && c0 + tx < cols) tile[k][tx] = xb[(r0 + k) * cols + c0 + tx];
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8)
+      if (c0 + k < cols && r0 + tx < rows) yb[(c0 + k) * rows + r0 + tx] = tile[tx][k];
+    __syncthreads();
+  }
 }
 
 // Same, 64 x 64 tiles moved with 128-bit accesses on both sides (rows % 4 == 0, cols % 4 == 0,
 // 16-byte aligned pointers): the NCHW -> NHWC pre-pass of the tensor-core convolution runs on this.
 __global__ void __launch_bounds__(256)
-transpose_2d_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int64_t cols) {
+transpose_2d_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t batch, int64_t rows, int64_t cols) {
   __shared__ float tile[64][65];
-  const float *xb = x + (int64_t)blockIdx.z * rows * cols;
-  float *yb = y + (int64_t)blockIdx.z * rows * cols;
   const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
   const int q = (threadIdx.x & 15) * 4, l = threadIdx.x >> 4;  // 16 float4 per tile row, 16 rows per pass
+  for (int64_t b = blockIdx.z; b < batch; b += gridDim.z) {  // grid.z is capped at 65535
+    const float *xb = x + b * rows * cols;
+    float *yb = y + b * rows * cols;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = l + 16 * i;
-    if (r0 + r < rows && c0 + q < cols) {
-      const float4 v = ld_stream4(xb + (r0 + r) * cols + c0 + q);
-      tile[r][q + 0] = v.x; tile[r][q + 1] = v.y; tile[r][q + 2] = v.z; tile[r][q + 3] = v.w;
+    for (int i = 0; i < 4; ++i) {
+      const int r = l + 16 * i;
+      if (r0 + r < rows && c0 + q < cols) {
+        const float4 v = ld_stream4(xb + (r0 + r) * cols + c0 + q);
+        tile[r][q + 0] = v.x; tile[r][q + 1] = v.y; tile[r][q + 2] = v.z; tile[r][q + 3] = v.w;
+      }
     }
-  }
-  __syncthreads();
+    __syncthreads();
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int c = l + 16 * i;  // input column = output row
-    if (c0 + c < cols && r0 + q < rows)
-      st_stream4(yb + (c0 + c) * rows + r0 + q, make_float4(tile[q + 0][c], tile[q + 1][c], tile[q + 2][c], tile[q + 3][c]));
+    for (int i = 0; i < 4; ++i) {
+      const int c = l + 16 * i;  // input column = output row
+      if (c0 + c < cols && r0 + q < rows)
+        st_stream4(yb + (c0 + c) * rows + r0 + q, make_float4(tile[q + 0][c], tile[q + 1][c], tile[q + 2][c], tile[q + 3][c]));
+    }
+    __syncthreads();
   }
 }
 
@@ -251,14 +257,16 @@ int launch_unary(cudaStream_t st, const float *x, float *y, int64_t numel) {
 }  // namespace
 
 int transpose_2d(cudaStream_t st, const float *x, float *y, int64_t batch, int64_t rows, int64_t cols) {
-  if (batch > 65535 || (rows + 31) / 32 > 65535) return fail(B200_EUNSUPPORTED, "transpose: extent too large");
+  if ((rows + 31) / 32 > 65535) return fail(B200_EUNSUPPORTED, "transpose: more than 65535 x 32 rows");
+  if (batch < 1 || rows < 1 || cols < 1) return B200_OK;
+  const unsigned gz = (unsigned)(batch < 65535 ? batch : 65535);  // larger batches loop inside the kernel
   if (rows % 4 == 0 && cols % 4 == 0 && aligned16(x) && aligned16(y)) {
-    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64), (unsigned)batch);
-    transpose_2d_vec_kernel<<<grid, 256, 0, st>>>(x, y, rows, cols);
+    dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64), gz);
+    transpose_2d_vec_kernel<<<grid, 256, 0, st>>>(x, y, batch, rows, cols);
     return check_launch("transpose_2d_vec");
   }
-  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), (unsigned)batch);
-  transpose_2d_kernel<<<grid, 256, 0, st>>>(x, y, rows, cols);
+  dim3 grid((unsigned)((cols + 31) / 32), (unsigned)((rows + 31) / 32), gz);
+  transpose_2d_kernel<<<grid, 256, 0, st>>>(x, y, batch, rows, cols);
   return check_launch("transpose_2d");
 }
 

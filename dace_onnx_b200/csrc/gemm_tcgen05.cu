@@ -1142,20 +1142,6 @@ int launch_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtensorMap 
   return fail(B200_EINVAL, "gemm(tc): no kernel for BN=%d", bn);
 }
 
-// OIHW filter -> [Cout][KH*KW][Cp] with the channel axis zero-padded to Cp (a multiple of 32): the
-// K order (tap, channel) in which the implicit GEMM walks the input.
-__global__ void __launch_bounds__(256)
-conv_repack_filter_kernel(const float *__restrict__ w, float *__restrict__ out, int64_t M, int C, int taps, int Cp) {
-  const int64_t total = M * taps * Cp;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % Cp);
-    const int64_t r = i / Cp;
-    const int tap = (int)(r % taps);
-    const int64_t m = r / taps;
-    out[i] = c < C ? w[(m * C + c) * taps + tap] : 0.f;
-  }
-}
-
 template <bool SPLIT3>
 int launch_conv_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   switch (bn) {
@@ -1363,35 +1349,12 @@ bool conv2d_tc_supported(const b200_conv_desc &d, const float *X) {
   return true;
 }
 
-size_t conv2d_tc_workspace_bytes(const b200_conv_desc &d) {
-  const size_t x_t = align256((size_t)d.N * d.H * d.W * d.C * 4);
-  const size_t w_t = align256((size_t)d.M * d.KH * d.KW * ((d.C + 31) / 32 * 32) * 4);
-  return x_t + w_t;
-}
-
-int conv2d_tc(cudaStream_t st, const b200_conv_desc &d, const float *X, const float *W, const float *bias, float *Y,
-              int64_t OH, int64_t OW, void *workspace, size_t workspace_bytes) {
-  if (workspace_bytes < conv2d_tc_workspace_bytes(d) || !workspace)
-    return fail(B200_EWORKSPACE, "conv: workspace of %zu bytes needed, %zu given", conv2d_tc_workspace_bytes(d),
-                workspace_bytes);
-  if (!aligned16(workspace)) return fail(B200_EINVAL, "conv: workspace must be 16-byte aligned");
+// Implicit GEMM on gemm_tc_kernel<..., CONV> from an NHWC copy of the input (`xt`) and the repacked filter
+// (`wt`: [M][KH*KW][Cp], channels zero-padded to a multiple of 32); writes NCHW. Any output-channel count.
+int conv2d_tc_gemm(cudaStream_t st, const b200_conv_desc &d, const float *xt, const float *wt, const float *bias,
+                   float *Y, int64_t OH, int64_t OW) {
   const int Cp = (int)((d.C + 31) / 32 * 32);
   const int taps = (int)(d.KH * d.KW);
-  float *xt = static_cast<float *>(workspace);
-  float *wt = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)d.N * d.H * d.W * d.C * 4));
-
-  // 1. X: NCHW -> NHWC (per image a [C, H*W] -> [H*W, C] transpose), so that the 32 channels of a
-  //    k-block are contiguous and filter-tap shifts move only the outer TMA coordinates.
-  if (int rc = transpose_2d(st, X, xt, d.N, d.C, d.H * d.W)) return rc;
-  // 2. filter repack
-  {
-    const int64_t total = d.M * taps * Cp;
-    int64_t g = (total + 255) / 256;
-    if (g > kNumSMs * 8) g = kNumSMs * 8;
-    conv_repack_filter_kernel<<<(unsigned)g, 256, 0, st>>>(W, wt, d.M, (int)d.C, taps, Cp);
-    if (int rc = check_launch("conv_repack_filter")) return rc;
-  }
-  // 3. implicit GEMM
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   const int bn = pick_bn(d.M, split3);
   CUtensorMap ma, mb;

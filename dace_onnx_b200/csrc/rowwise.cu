@@ -8,6 +8,7 @@
 // order of the reference's pure expansions (max, subtract, exp, sum, divide; mean, centred
 // second moment, sqrt, divide) with IEEE expf/logf/sqrtf and true division (no fast-math).
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -230,6 +231,71 @@ layernorm_warp_vec_kernel(const float *__restrict__ x, const float *__restrict__
   }
 }
 
+// The same arithmetic as a persistent kernel: each warp walks rows with a grid stride and issues the 128-bit
+// loads of its NEXT row before it reduces and stores the current one, so every warp keeps a full row of loads in
+// flight through its reduction and store phases (the one-row-per-warp form above has nothing in flight then, and
+// pays a CTA launch per eight rows). Grid = a multiple of the SM count.
+template <int VPT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
+layernorm_warp_pipe_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
+                           const float *__restrict__ beta, float *__restrict__ y, int64_t rows, int len, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
+  int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int nvec = len >> 2;
+  const float inv_len = 1.0f / (float)len;
+  float4 v[VPT], nx[VPT];
+  if (row < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (lane + 32 * i < nvec) v[i] = ld_stream4(x + row * len + 4 * (lane + 32 * i));
+  }
+  for (; row < rows; row += nwarps) {
+    const int64_t next = row + nwarps;
+    if (next < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+        if (lane + 32 * i < nvec) nx[i] = ld_stream4(x + next * len + 4 * (lane + 32 * i));
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (lane + 32 * i < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float mean = warp_sum(s) / (float)len;  // ReduceMean
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (lane + 32 * i < nvec) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;                   // Sub
+        q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);  // Pow 2
+      }
+    }
+    const float var = warp_sum(q) / (float)len;  // ReduceMean
+    const float inv = 1.0f / sqrtf(var + eps);   // Add eps, Sqrt, and Div as one reciprocal per row
+    float *yr = y + row * len;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float4 o;
+        o.x = v[i].x * inv; o.y = v[i].y * inv; o.z = v[i].z * inv; o.w = v[i].w * inv;
+        if (gamma) {
+          const float4 g = __ldg(reinterpret_cast<const float4 *>(gamma + 4 * c));
+          o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;  // Mul
+        }
+        if (beta) {
+          const float4 b = __ldg(reinterpret_cast<const float4 *>(beta + 4 * c));
+          o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;  // Add
+        }
+        st_stream4(yr + 4 * c, o);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) v[i] = nx[i];
+    (void)inv_len;
+  }
+}
+
 // CTA-per-row fallback for any length / alignment (row cached in shared memory when it fits).
 __global__ void __launch_bounds__(512)
 layernorm_block_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
@@ -383,6 +449,18 @@ extern "C" B200_API int b200_layernorm_f32(void *stream, const float *x, const f
   if (!x || !y) return fail(B200_EINVAL, "layernorm: null pointer");
   const bool vec_ok = (len % 4 == 0) && aligned16(x) && aligned16(y) && (!gamma || aligned16(gamma)) &&
                       (!beta || aligned16(beta));
+  static const int variant = getenv("B200_LN_VARIANT") ? atoi(getenv("B200_LN_VARIANT")) : 0;
+  if (vec_ok && len <= 1024 && len > 256 && variant > 0 && rows >= 8 * kNumSMs) {
+    const unsigned grid = (unsigned)(kNumSMs * variant);
+    const int nvec = (int)(len >> 2);
+#define B200_LN_PIPE(V)                                                                          \
+  layernorm_warp_pipe_kernel<V><<<grid, kWarpsPerCta * 32, 0, st>>>(x, gamma, beta, y, rows, (int)len, eps)
+    if (nvec <= 128) B200_LN_PIPE(4);
+    else if (nvec <= 192) B200_LN_PIPE(6);
+    else B200_LN_PIPE(8);
+#undef B200_LN_PIPE
+    return check_launch("layernorm_warp_pipe");
+  }
   if (vec_ok && len <= 2048) {
     const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
     const int nvec = (int)(len >> 2);

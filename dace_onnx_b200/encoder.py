@@ -88,6 +88,10 @@ class BertEncoderB200:
             self._buf_key = key
         return self._buf
 
+    def release_buffers(self):
+        """Drop the scratch and staging buffers (they are re-created on the next call)."""
+        self._buf_key = self._buf = self._io = None
+
     def _score_buffers(self, mb, seq):
         """[mb, heads, S, S] scores and probabilities, only needed by the unfused attention path."""
         buf = self._buf
@@ -161,8 +165,25 @@ class BertEncoderB200:
             trans_b=False, math_mode=mm))
 
     # -- whole encoder ------------------------------------------------------------------------------
-    def forward_device(self, x, out=None):
-        """x: [B, S, hidden] fp32 on this encoder's device. Returns [B, S, hidden] on the device."""
+    def device_chunks(self, bsz, tail_chunks=1):
+        """[(lo, n), ...]: the pieces of the batch in the order forward_device completes them -- one per
+        micro-batch, the last micro-batch's final layer cut into `tail_chunks` pieces (so that whatever consumes
+        finished pieces, e.g. the output all-gather, has only a small last piece left when the forward ends)."""
+        mb = min(self.micro_batch, max(bsz, 1))
+        out = []
+        for b0 in range(0, bsz, mb):
+            b = min(mb, bsz - b0)
+            if b0 + b >= bsz and tail_chunks > 1 and b >= 8 * tail_chunks:
+                cb = -(-b // tail_chunks)
+                out.extend((b0 + c0, min(cb, b - c0)) for c0 in range(0, b, cb))
+            else:
+                out.append((b0, b))
+        return out
+
+    def forward_device(self, x, out=None, tail_chunks=1, on_chunk=None):
+        """x: [B, S, hidden] fp32 on this encoder's device. Returns [B, S, hidden] on the device.
+        `on_chunk(lo, n)` is called (on the host, in stream order) after the launches that complete samples
+        [lo, lo+n) of `out`; the pieces are those of device_chunks(B, tail_chunks)."""
         if x.device != self.device or x.dtype != torch.float32 or x.dim() != 3 or x.shape[2] != self.hidden:
             raise ValueError("expected a float32 [B, S, %d] tensor on %s" % (self.hidden, self.device))
         x = x.contiguous()
@@ -171,13 +192,20 @@ class BertEncoderB200:
             out = torch.empty_like(x)
         mb = min(self.micro_batch, max(bsz, 1))
         buf = self._buffers(mb, seq)
+        pieces = self.device_chunks(bsz, tail_chunks)
         for b0 in range(0, bsz, mb):
             b = min(mb, bsz - b0)
             cur = x[b0:b0 + b]
+            mine = [(lo, n) for lo, n in pieces if b0 <= lo < b0 + b]
             for li, w in enumerate(self.layers):
                 last = li + 1 == len(self.layers)
-                dst = out[b0:b0 + b] if last else (buf["ping"][:b] if li % 2 == 0 else buf["pong"][:b])
-                cur = self._layer(cur, dst, w, buf, b, seq)
+                if last:
+                    for lo, n in mine:
+                        self._layer(cur[lo - b0:lo - b0 + n], out[lo:lo + n], w, buf, n, seq)
+                        if on_chunk is not None:
+                            on_chunk(lo, n)
+                else:
+                    cur = self._layer(cur, buf["ping"][:b] if li % 2 == 0 else buf["pong"][:b], w, buf, b, seq)
         return out
 
     def __call__(self, x_host, out_host=None):
@@ -188,22 +216,8 @@ class BertEncoderB200:
         torch.cuda.current_stream(self.device).synchronize()
         return out_host
 
-    def forward_host(self, x_host, out_host, out_device=None):
-        """Host buffers in and out, copies overlapped with compute.
-
-        The batch moves in micro-batches through three streams: host->device copies on a copy-in
-        stream into two alternating staging buffers, the layers on the current stream, and
-        device->host copies of finished micro-batches on a copy-out stream, ordered by events. With
-        pinned host tensors the copies of micro-batch i+1 and i-1 run while micro-batch i computes.
-        `out_device` ([B, S, hidden] on the device, optional) also keeps the result resident, e.g.
-        for the output all-gather. Returns after enqueueing; the caller synchronises the current
-        stream (the last device->host copy is joined into it).
-        """
-        if x_host.dim() != 3 or x_host.shape[2] != self.hidden or x_host.dtype != torch.float32:
-            raise ValueError("expected a float32 [B, S, %d] host tensor" % self.hidden)
-        if tuple(out_host.shape) != tuple(x_host.shape):
-            raise ValueError("out_host must have the input's shape")
-        bsz, seq, _ = x_host.shape
+    def host_chunks(self, bsz):
+        """[(lo, n), ...]: the micro-batches forward_host moves and computes, in order."""
         mb = min(self.micro_batch, max(bsz, 1))
         if 64 <= bsz <= self.micro_batch:
             mb = (bsz + 1) // 2  # a batch that fits one micro-batch still moves in two, so that copies overlap compute
@@ -220,6 +234,27 @@ class BertEncoderB200:
                 b = min(mb, bsz - b0)
             bounds.append((b0, b))
             b0 += b
+        return bounds
+
+    def forward_host(self, x_host, out_host, out_device=None, on_chunk=None):
+        """Host buffers in and out, copies overlapped with compute.
+
+        The batch moves in micro-batches through three streams: host->device copies on a copy-in
+        stream into two alternating staging buffers, the layers on the current stream, and
+        device->host copies of finished micro-batches on a copy-out stream, ordered by events. With
+        pinned host tensors the copies of micro-batch i+1 and i-1 run while micro-batch i computes.
+        `out_device` ([B, S, hidden] on the device, optional) also keeps the result resident, e.g.
+        for the output all-gather; `on_chunk(lo, n)` is called after the launches that complete samples
+        [lo, lo+n) of it (the pieces are host_chunks(B)). Returns after enqueueing; the caller synchronises the current
+        stream (the last device->host copy is joined into it).
+        """
+        if x_host.dim() != 3 or x_host.shape[2] != self.hidden or x_host.dtype != torch.float32:
+            raise ValueError("expected a float32 [B, S, %d] host tensor" % self.hidden)
+        if tuple(out_host.shape) != tuple(x_host.shape):
+            raise ValueError("out_host must have the input's shape")
+        bsz, seq, _ = x_host.shape
+        bounds = self.host_chunks(bsz)
+        mb = max(b for _, b in bounds)
         buf = self._buffers(mb, seq)
         if self._io is None or self._io[0] != (mb, seq):
             e = lambda: torch.empty(mb, seq, self.hidden, device=self.device, dtype=torch.float32)  # noqa: E731
@@ -246,6 +281,8 @@ class BertEncoderB200:
                 nxt = dst if last else (buf["ping"][:b] if li % 2 == 0 else buf["pong"][:b])
                 cur = self._layer(cur, nxt, w, buf, b, seq)
             ev_done.append(main.record_event())
+            if on_chunk is not None:
+                on_chunk(b0, b)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_done[i])
                 out_host[b0:b0 + b].copy_(dst, non_blocking=True)

@@ -18,9 +18,20 @@ def mlp_forward(x, params, math_mode=None):
     return ops.logsoftmax(h, axis=1)
 
 
+def prepare_conv_stack(params, math_mode=None):
+    """Set-up of conv_stack_forward: each layer's filter repacked once (ops.PreparedConv)."""
+    return [ops.PreparedConv(w, b, pads=(1, 1, 1, 1), relu=True, math_mode=math_mode) for w, b in params]
+
+
 def conv_stack_forward(x, params, math_mode=None, workspace=None):
-    """x: [N, C, H, W]; params: [(W[M, C, 3, 3], b[M]), ...]."""
-    h = x
-    for w, b in params:
-        h = ops.conv2d(h, w, b, pads=(1, 1, 1, 1), relu=True, workspace=workspace, math_mode=math_mode)
+    """x: [N, C, H, W]; params: [(W[M, C, 3, 3], b[M]), ...] or the result of prepare_conv_stack. Returns NCHW.
+
+    Between two consecutive convolutions the activations stay in the [N, H, W, C] layout the tensor-core kernel
+    reads and writes natively; only the stack's input and output pay the NCHW <-> NHWC change."""
+    layers = params if params and isinstance(params[0], ops.PreparedConv) else prepare_conv_stack(params, math_mode)
+    h, nhwc = x, False
+    for i, conv in enumerate(layers):
+        keep = i + 1 < len(layers) and conv.nhwc_ok and layers[i + 1].nhwc_ok
+        h = conv(h, x_nhwc=nhwc, y_nhwc=keep, workspace=workspace)
+        nhwc = keep
     return h

@@ -235,6 +235,77 @@ def conv2d(X, W, B=None, out=None, *, pads=(0, 0, 0, 0), strides=(1, 1), dilatio
     return out
 
 
+class PreparedConv:
+    """A convolution whose constant work is done once: the filter repacked (and, in fp32x3 mode, split) into a
+    device buffer by b200_conv2d_prepare_filter_f32, the way the reference's cuDNN expansion builds its descriptors
+    in the SDFG init hook (cudnn_implementations.py:281-301). Calls then run b200_conv2d_prepared_f32.
+
+    W: [M, C, KH, KW], B: [M] or None (both CUDA fp32). `nhwc_ok` says whether this convolution can take / produce
+    [N, H, W, C] tensors, which saves the layout change between the convolutions of a stack."""
+
+    def __init__(self, W, B=None, *, pads=(0, 0, 0, 0), strides=(1, 1), dilations=(1, 1), group=1, relu=False,
+                 math_mode=None):
+        W = _contig(W, "W")
+        if W.dim() != 4:
+            raise NotImplementedError("Conv: only 2-D convolutions")
+        if group != 1 or tuple(dilations) != (1, 1):
+            raise NotImplementedError("Conv: group and dilations must be 1")
+        if pads[0] != pads[2] or pads[1] != pads[3]:
+            raise NotImplementedError("Conv: padding must be symmetric")
+        if B is None and relu:
+            raise ValueError("Conv: relu fusion needs a bias operand")
+        self.M, self.C, self.KH, self.KW = (int(v) for v in W.shape)
+        self.pads, self.strides = (int(pads[0]), int(pads[1])), (int(strides[0]), int(strides[1]))
+        self.bias = _contig(B, "B") if B is not None else None
+        self.epilogue = EPI_NONE if B is None else (EPI_BIAS_RELU if relu else EPI_BIAS)
+        self.mode = _math(math_mode)
+        lib = _lib.load()
+        d = self.desc(1, 1, 1)
+        self.nhwc_ok = bool(lib.b200_conv2d_nhwc_supported(ctypes.byref(d)))
+        nbytes = int(lib.b200_conv2d_filter_bytes(ctypes.byref(d)))
+        self.filter = torch.empty(max(nbytes, 16), device=W.device, dtype=torch.uint8)
+        check(lib.b200_conv2d_prepare_filter_f32(_stream(), ctypes.byref(d), _ptr(W), _ptr(self.filter), nbytes))
+        self._ws = None
+
+    def desc(self, n, h, w):
+        return ConvDesc(n, self.C, h, w, self.M, self.KH, self.KW, self.pads[0], self.pads[1], self.strides[0],
+                        self.strides[1], self.epilogue, self.mode)
+
+    def out_hw(self, h, w):
+        return ((h + 2 * self.pads[0] - self.KH) // self.strides[0] + 1,
+                (w + 2 * self.pads[1] - self.KW) // self.strides[1] + 1)
+
+    def __call__(self, X, out=None, *, x_nhwc=False, y_nhwc=False, workspace=None):
+        """X: [N, C, H, W], or [N, H, W, C] with x_nhwc. Returns [N, M, OH, OW], or [N, OH, OW, M] with y_nhwc."""
+        X = _contig(X, "X")
+        if X.dim() != 4:
+            raise NotImplementedError("Conv: only 2-D convolutions")
+        n, c, h, w = (X.shape[0], X.shape[3], X.shape[1], X.shape[2]) if x_nhwc else X.shape
+        if c != self.C:
+            raise ValueError("Conv: channel mismatch")
+        oh, ow = self.out_hw(h, w)
+        oshape = (n, oh, ow, self.M) if y_nhwc else (n, self.M, oh, ow)
+        if out is None:
+            out = torch.empty(oshape, device=X.device, dtype=torch.float32)
+        elif tuple(out.shape) != oshape or not out.is_contiguous():
+            raise ValueError("Conv: out must be contiguous with shape %s" % (oshape,))
+        flags = (_lib.CONV_X_NHWC if x_nhwc else 0) | (_lib.CONV_Y_NHWC if y_nhwc else 0)
+        lib = _lib.load()
+        d = self.desc(n, h, w)
+        need = int(lib.b200_conv2d_prepared_workspace_bytes(ctypes.byref(d), flags))
+        if need:
+            if workspace is None or workspace.numel() * workspace.element_size() < need:
+                if self._ws is None or self._ws.numel() < need or self._ws.device != X.device:
+                    self._ws = torch.empty(need, device=X.device, dtype=torch.uint8)
+                workspace = self._ws
+        else:
+            workspace = None
+        ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+        check(lib.b200_conv2d_prepared_f32(_stream(), ctypes.byref(d), flags, _ptr(X), _ptr(self.filter),
+                                           _ptr(self.bias), _ptr(out), _ptr(workspace), ws_bytes))
+        return out
+
+
 # ------------------------------------------------------------------------------------------------
 # row-wise
 # ------------------------------------------------------------------------------------------------

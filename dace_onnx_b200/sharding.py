@@ -70,6 +70,77 @@ def all_gather_batch(local, total, out=None, group=None):
     return out
 
 
+class OverlappedGather:
+    """All-gather of the outputs piece by piece, each piece on a side stream as soon as the forward pass has
+    finished it, so that only the last piece's transfer is not hidden behind compute.
+
+    Every rank cuts its shard into the same `chunks` = [(lo, n), ...] (local sample ranges in the order the
+    forward pass completes them). Piece c of all ranks lands in one contiguous block of the gathered tensor, so
+    each piece is a single all_gather_into_tensor straight into its place, without staging copies:
+
+        gathered[world * lo_c + r * n_c + j] = rank r's local sample lo_c + j
+
+    i.e. the batch is dealt to the ranks piece-cyclically instead of in one contiguous slab per rank
+    (`global_rows` gives a rank's rows; with a single piece it is exactly shard_bounds). Samples are independent
+    on this path, so which rank computes which sample does not change any result. Needs total % world == 0."""
+
+    def __init__(self, total, chunks, group=None, timeline=None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if total % self.world:
+            raise ValueError("OverlappedGather needs equal shards (total %d, world %d)" % (total, self.world))
+        self.total, self.local, self.group = total, total // self.world, group
+        pos = 0
+        for lo, n in chunks:
+            if lo != pos or n < 1:
+                raise ValueError("chunks must tile [0, %d) in order, got %s" % (self.local, chunks))
+            pos += n
+        if pos != self.local:
+            raise ValueError("chunks cover %d of %d local samples" % (pos, self.local))
+        self.chunks = {lo: n for lo, n in chunks}
+        self.timeline = timeline   # when a list: (start_event, end_event, bytes) per collective
+        self._side = None
+
+    def global_rows(self, rank=None):
+        """Rows of the gathered tensor that `rank` computes, in the order of its local samples."""
+        r = self.rank if rank is None else rank
+        rows = []
+        for lo, n in sorted(self.chunks.items()):
+            rows.extend(range(self.world * lo + r * n, self.world * lo + (r + 1) * n))
+        return rows
+
+    def chunk_done(self, y_local, out, lo, n):
+        """Call when local samples [lo, lo+n) of y_local are final (in stream order on the current stream)."""
+        if self.chunks.get(lo) != n:
+            raise ValueError("piece (%d, %d) is not in the plan" % (lo, n))
+        dst = out[self.world * lo:self.world * (lo + n)]
+        src = y_local[lo:lo + n]
+        if self.world == 1:
+            if dst.data_ptr() != src.data_ptr():
+                dst.copy_(src)
+            return
+        if not y_local.is_cuda:
+            dist.all_gather_into_tensor(dst, src.contiguous(), group=self.group)
+            return
+        main = torch.cuda.current_stream(y_local.device)
+        if self._side is None:
+            self._side = torch.cuda.Stream(y_local.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            if self.timeline is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            dist.all_gather_into_tensor(dst, src, group=self.group)
+            if self.timeline is not None:
+                e1.record()
+                self.timeline.append((e0, e1, dst.numel() * dst.element_size()))
+
+    def finish(self, device=None):
+        """Join the side stream into the current stream: afterwards `out` is complete in stream order."""
+        if self._side is not None:
+            torch.cuda.current_stream(device).wait_stream(self._side)
+
+
 def sharded_forward(forward, x_local, total, out=None, group=None):
     """Run `forward` on this rank's shard and all-gather the result."""
     return all_gather_batch(forward(x_local), total, out=out, group=group)

@@ -6,7 +6,9 @@
  * Conventions (all entry points):
  *   - every tensor pointer is a DEVICE pointer to contiguous row-major fp32 unless a stride
  *     argument says otherwise; the caller owns every buffer, the library never allocates,
- *     frees or caches device memory, and never writes its inputs;
+ *     frees or caches device memory, and never writes its inputs (one documented exception:
+ *     b200_conv2d_static_f32 keeps its scratch in a fixed array inside the library and caches that
+ *     array's address per device);
  *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered on it, the
  *     library never synchronises the host and never uses the default stream implicitly;
  *   - the return value is 0 on success or a negative B200_E* code; the message is available
@@ -152,6 +154,31 @@ typedef struct b200_conv_desc {
 B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc);
 B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
                     const float *bias, float *Y, void *workspace, size_t workspace_bytes);
+
+/* The same convolution with the constant work taken out of the call, the way the reference's cuDNN expansion sets
+ * its filter / tensor descriptors up once in the SDFG init hook and only runs the convolution per call
+ * (daceml/onnx/op_implementations/cudnn_implementations.py:281-301).
+ *   b200_conv2d_prepare_filter_f32 repacks the OIHW filter W once (for B200_MATH_FP32X3 it also splits it into
+ *     its two TF32 halves) into `filter`, b200_conv2d_filter_bytes(desc) bytes of 16-byte aligned device memory
+ *     the caller keeps for as long as it runs this convolution; desc->N is ignored by both.
+ *   b200_conv2d_prepared_f32 runs one convolution from a prepared filter. `flags` says in which layout the
+ *     activations are: 0 = X and Y are NCHW as in ONNX; B200_CONV_X_NHWC = X is [N,H,W,C]; B200_CONV_Y_NHWC = Y is
+ *     written as [N,OH,OW,M]. Between two convolutions of a stack the NHWC form saves the layout change the tensor
+ *     cores need (only graph inputs / outputs pay it). NHWC is taken where b200_conv2d_nhwc_supported(desc) is 1
+ *     (stride 1, C a multiple of 4 and >= 16, at most 64 output channels whose filter fits in shared memory, a
+ *     tensor-core math mode); elsewhere a call with either flag returns B200_EUNSUPPORTED.
+ *     `workspace`: b200_conv2d_prepared_workspace_bytes(desc, flags) bytes (0 with B200_CONV_X_NHWC).
+ * Results are those of b200_conv2d_f32 (which is prepare + run on its own workspace). */
+#define B200_CONV_X_NHWC 1
+#define B200_CONV_Y_NHWC 2
+B200_API size_t b200_conv2d_filter_bytes(const b200_conv_desc *desc);
+B200_API int b200_conv2d_prepare_filter_f32(void *stream, const b200_conv_desc *desc, const float *W, void *filter,
+                                            size_t filter_bytes);
+B200_API int b200_conv2d_nhwc_supported(const b200_conv_desc *desc);
+B200_API size_t b200_conv2d_prepared_workspace_bytes(const b200_conv_desc *desc, int flags);
+B200_API int b200_conv2d_prepared_f32(void *stream, const b200_conv_desc *desc, int flags, const float *X,
+                                      const void *filter, const float *bias, float *Y, void *workspace,
+                                      size_t workspace_bytes);
 
 /* Convolution for callers that cannot allocate device memory. No counterpart in the reference:
  * every GPU library call there gets its workspace from an SDFG init hook (cudaMalloc in

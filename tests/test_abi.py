@@ -55,6 +55,29 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.b200_gemm_f32(None, ctypes.byref(d), one, one, None, None, one) == _lib.EINVAL
 
 
+def test_prepared_conv_argument_errors_without_a_gpu():
+    lib = _lib.load()
+    d = _lib.ConvDesc(2, 64, 8, 8, 64, 3, 3, 1, 1, 1, 1, 0, _lib.MATH_TF32)
+    one = ctypes.c_void_p(256)
+    assert lib.b200_conv2d_nhwc_supported(ctypes.byref(d)) == 1
+    assert lib.b200_conv2d_filter_bytes(ctypes.byref(d)) == 64 * 9 * 64 * 4
+    assert lib.b200_conv2d_prepared_workspace_bytes(ctypes.byref(d), 0) == 2 * 64 * 8 * 8 * 4
+    assert lib.b200_conv2d_prepared_workspace_bytes(ctypes.byref(d), _lib.CONV_X_NHWC) == 0
+    assert lib.b200_conv2d_prepared_f32(None, ctypes.byref(d), 4, one, one, None, one, None, 0) == _lib.EINVAL
+    assert lib.b200_conv2d_prepared_f32(None, ctypes.byref(d), 0, one, one, None, one, None, 0) == _lib.EWORKSPACE
+    assert lib.b200_conv2d_prepare_filter_f32(None, ctypes.byref(d), one, one, 16) == _lib.EWORKSPACE
+    d3 = _lib.ConvDesc(2, 64, 8, 8, 64, 3, 3, 1, 1, 1, 1, 0, _lib.MATH_FP32X3)
+    assert lib.b200_conv2d_filter_bytes(ctypes.byref(d3)) == 3 * 64 * 9 * 64 * 4     # raw, hi, lo
+    wide = _lib.ConvDesc(2, 64, 8, 8, 128, 3, 3, 1, 1, 1, 1, 0, _lib.MATH_TF32)       # 128 output channels
+    assert lib.b200_conv2d_nhwc_supported(ctypes.byref(wide)) == 0
+    assert lib.b200_conv2d_prepared_f32(None, ctypes.byref(wide), _lib.CONV_Y_NHWC, one, one, None, one, one,
+                                        1 << 30) == _lib.EUNSUPPORTED
+    big = _lib.ConvDesc(2, 512, 8, 8, 64, 3, 3, 1, 1, 1, 1, 0, _lib.MATH_TF32)        # filter half beyond shared memory
+    assert lib.b200_conv2d_nhwc_supported(ctypes.byref(big)) == 0
+    # the one-call entry point still sizes its workspace as [NHWC copy | prepared filter]
+    assert lib.b200_conv2d_workspace_bytes(ctypes.byref(d)) == 2 * 64 * 8 * 8 * 4 + 64 * 9 * 64 * 4
+
+
 def test_ops_refuse_cpu_tensors():
     import pytest
     import torch

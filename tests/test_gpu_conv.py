@@ -59,3 +59,64 @@ def test_conv_stride_and_errors(cuda):
         ops.conv2d(x.cuda(), w.cuda(), group=2)
     with pytest.raises(ValueError):
         ops.conv2d(x.cuda(), torch.rand(5, 3, 3, 3).cuda())
+
+
+@pytest.mark.parametrize("mode,rtol,atol", [("fp32x3", RTOL, ATOL), ("tf32", TF32_RTOL, TF32_ATOL)])
+@pytest.mark.parametrize("n,c,h,w,m,k,pad", [(3, 64, 56, 56, 64, 3, 1), (2, 32, 20, 13, 48, 3, 1), (1, 16, 9, 9, 16, 1, 0),
+                                             (5, 64, 7, 7, 24, 3, 0), (2, 48, 17, 30, 64, 5, 2), (1, 96, 12, 12, 33, 3, 1)])
+def test_prepared_conv_layouts(n, c, h, w, m, k, pad, mode, rtol, atol, cuda):
+    """b200_conv2d_prepared_f32 in all four layout combinations against the oracle (NCHW) -- odd image sizes
+    (8x8 block tails), output-channel counts that are not multiples of 16 or 32, 1x1 / 5x5 filters."""
+    g = torch.Generator().manual_seed(n * 100 + c + m)
+    x = torch.rand(n, c, h, w, generator=g)
+    wt = (torch.rand(m, c, k, k, generator=g) * 2 - 1) / (c * k * k) ** 0.5
+    b = torch.rand(m, generator=g) - 0.5
+    ref = po.Relu(po.Conv(x, wt, b, pads=(pad,) * 4))
+    conv = ops.PreparedConv(wt.cuda(), b.cuda(), pads=(pad,) * 4, relu=True, math_mode=mode)
+    assert conv.nhwc_ok
+    xd = x.cuda()
+    xn = xd.permute(0, 2, 3, 1).contiguous()
+    close(conv(xd), ref, rtol, atol)
+    close(conv(xd, y_nhwc=True).permute(0, 3, 1, 2), ref, rtol, atol)
+    close(conv(xn, x_nhwc=True), ref, rtol, atol)
+    close(conv(xn, x_nhwc=True, y_nhwc=True).permute(0, 3, 1, 2), ref, rtol, atol)
+    # no bias, no relu
+    conv0 = ops.PreparedConv(wt.cuda(), None, pads=(pad,) * 4, math_mode=mode)
+    close(conv0(xn, x_nhwc=True, y_nhwc=True).permute(0, 3, 1, 2), po.Conv(x, wt, None, pads=(pad,) * 4), rtol, atol)
+
+
+def test_prepared_conv_outside_the_resident_filter_kernel(cuda):
+    g = torch.Generator().manual_seed(81)
+    # 128 output channels: general tensor-core kernel, NCHW only
+    x, w, b = torch.rand(2, 32, 10, 10, generator=g), torch.rand(128, 32, 3, 3, generator=g) - 0.5, torch.rand(128, generator=g)
+    conv = ops.PreparedConv(w.cuda(), b.cuda(), pads=(1, 1, 1, 1))
+    assert not conv.nhwc_ok
+    close(conv(x.cuda()), po.Conv(x, w, b, pads=(1, 1, 1, 1)))
+    with pytest.raises(ops._lib.B200Error) as e:
+        conv(x.cuda().permute(0, 2, 3, 1).contiguous(), x_nhwc=True)
+    assert e.value.code == ops._lib.EUNSUPPORTED
+    # strided, 3 input channels: CUDA-core kernel behind the same entry points
+    x, w = torch.rand(2, 3, 13, 13, generator=g), torch.rand(5, 3, 3, 3, generator=g) - 0.5
+    conv = ops.PreparedConv(w.cuda(), None, pads=(1, 1, 1, 1), strides=(2, 2))
+    close(conv(x.cuda()), torch.nn.functional.conv2d(x, w, stride=2, padding=1), rtol=1e-5, atol=1e-5)
+    # the plain fp32 mode
+    x, w = torch.rand(2, 64, 9, 9, generator=g), torch.rand(64, 64, 3, 3, generator=g) - 0.5
+    conv = ops.PreparedConv(w.cuda(), None, pads=(1, 1, 1, 1), math_mode="fp32")
+    assert not conv.nhwc_ok
+    close(conv(x.cuda()), po.Conv(x, w, None, pads=(1, 1, 1, 1)))
+
+
+def test_conv_stack_keeps_nhwc_between_layers(cuda):
+    from dace_onnx_b200 import graphs
+    params = po.make_conv_params(3, channels=64, layers=3)
+    x = torch.rand(5, 64, 28, 28, generator=torch.Generator().manual_seed(82))
+    layers = graphs.prepare_conv_stack([(w.cuda(), b.cuda()) for w, b in params])
+    assert all(c.nhwc_ok for c in layers)
+    out = graphs.conv_stack_forward(x.cuda(), layers)
+    close(out, po.conv_stack_forward(x, params))
+    assert torch.equal(out, graphs.conv_stack_forward(x.cuda(), layers))  # prepared filters are reusable
+
+
+def test_transpose_batch_beyond_grid_limit(cuda):
+    x = torch.randn(70000, 4, 8, generator=torch.Generator().manual_seed(83)).cuda()
+    assert torch.equal(ops.transpose_last2(x), x.transpose(1, 2).contiguous())
