@@ -52,6 +52,7 @@ SIGNATURES = {
     "b200_version": (c_int, []),
     "b200_last_error_string": (c_char_p, []),
     "b200_device_status": (c_int, []),
+    "b200_selftest_wait_expiry": (c_int, [c_void_p, c_int64]),
     "b200_gemm_f32": (c_int, [c_void_p, POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200_gemm_workspace_bytes": (c_size_t, [POINTER(GemmDesc)]),
     "b200_gemm_ws_f32": (c_int, [c_void_p, POINTER(GemmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

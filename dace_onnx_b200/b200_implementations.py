@@ -141,7 +141,10 @@ def gemm_env_code(a_shape, b_shape, ws_name, trans_b=False, bias=False, mode=Non
         b200_gemm_desc d = {init};
         __state->{ws}_bytes = b200_gemm_workspace_bytes(&d);
         __state->{ws} = nullptr;
-        if (__state->{ws}_bytes) cudaMalloc(&__state->{ws}, __state->{ws}_bytes);
+        if (__state->{ws}_bytes && cudaMalloc(&__state->{ws}, __state->{ws}_bytes) != cudaSuccess) {{
+            fprintf(stderr, "b200: cannot allocate %zu bytes of GEMM workspace\\n", __state->{ws}_bytes);
+            abort();
+        }}
     }}
 """.format(init=init_list, ws=ws_name)
     fini = "\n    if (__state->{ws}) cudaFree(__state->{ws});\n".format(ws=ws_name)
@@ -174,7 +177,10 @@ def conv_env_code(x_shape, w_shape, pads, strides, ws_name, mode=None):
         b200_conv_desc d = {{{n}, {c}, {h}, {w}, {m}, {kh}, {kw}, {ph}, {pw}, {sh}, {sw}, 0, {mode}}};
         __state->{ws}_bytes = b200_conv2d_workspace_bytes(&d);
         __state->{ws} = nullptr;
-        if (__state->{ws}_bytes) cudaMalloc(&__state->{ws}, __state->{ws}_bytes);
+        if (__state->{ws}_bytes && cudaMalloc(&__state->{ws}, __state->{ws}_bytes) != cudaSuccess) {{
+            fprintf(stderr, "b200: cannot allocate %zu bytes of convolution workspace\\n", __state->{ws}_bytes);
+            abort();
+        }}
     }}
 """.format(n=n, c=c, h=h, w=w, m=m, kh=kh, kw=kw, ph=int(pads[0]), pw=int(pads[1]), sh=int(strides[0]),
            sw=int(strides[1]), mode=mode, ws=ws_name)
@@ -254,7 +260,7 @@ def _register():
     from dace.libraries.standard import CUDA
     from daceml.onnx.forward_implementation_abc import ONNXForward
     from daceml.onnx.op_implementations.utils import empty_sdfg_for_node, op_implementation
-    from daceml.util.utils import in_desc_with_name, is_desc_contiguous, out_desc_with_name
+    from daceml.util.utils import in_desc_with_name, is_cuda, is_desc_contiguous, out_desc_with_name
 
     @dace.library.environment
     class B200Ops:
@@ -273,9 +279,24 @@ def _register():
         init_code = ""
         finalize_code = ""
 
+    def on_gpu(desc):
+        # The kernels take device pointers: a descriptor in host (or FPGA) storage -- an SDFG built with
+        # cuda=False -- is not ours (daceml/util/utils.py:236-245 is the reference's test for a GPU array).
+        try:
+            return is_cuda(desc.storage)
+        except ValueError:
+            return False
+
     def static_f32(desc):
-        return (desc.dtype == dace.float32 and is_desc_contiguous(desc)
+        return (desc.dtype == dace.float32 and is_desc_contiguous(desc) and on_gpu(desc)
                 and not any(dace.symbolic.issymbolic(s) for s in desc.shape))
+
+    def unique_id(node, state, sdfg):
+        # one state field per node instance: node name + SDFG id + state id + node id, as the reference's cuDNN
+        # expansion names its descriptors (cudnn_implementations.py:205-207); two nodes with the same label in
+        # different nested SDFGs must not share a workspace field
+        name = "".join(ch if ch.isalnum() else "_" for ch in str(getattr(node, "name", None) or node.label))
+        return "b200_ws_%s_%s_%s_%s" % (name, sdfg.sdfg_id, sdfg.node_id(state), state.node_id(node))
 
     def descs(node, state, sdfg, ins, outs):
         found = {}
@@ -311,7 +332,7 @@ def _register():
             @staticmethod
             def forward(node, state, sdfg):
                 d = descs(node, state, sdfg, ins, outs)
-                code, env = build(node, d)
+                code, env = build(node, d, unique_id(node, state, sdfg))
                 nsdfg, env = emit(node, state, sdfg, code, ins, outs, env or B200Ops)
                 Impl.environments = [env]
                 return nsdfg
@@ -320,11 +341,10 @@ def _register():
         Impl.__doc__ = "b200 expansion of ONNX%s through libb200ops." % op
         _REGISTERED[op] = op_implementation(op=op, name="b200")(Impl)
 
-    def gemm_build(node, d, trans_b, bias):
+    def gemm_build(node, d, ws, trans_b, bias):
         # fp32-accurate mode: the node gets device scratch from the SDFG state, like the cuDNN expansion
         if math_mode() != 0:
             return tasklet_matmul(d["A"].shape, d["B"].shape, node.label, trans_b=trans_b, bias=bias), None
-        ws = "b200_ws_%s" % "".join(ch if ch.isalnum() else "_" for ch in node.label)
         fields, init, fini = gemm_env_code(d["A"].shape, d["B"].shape, ws, trans_b=trans_b, bias=bias)
 
         class GemmEnv(B200Ops):
@@ -338,16 +358,15 @@ def _register():
     make("MatMul", ["A", "B"], ["Y"],
          lambda node, d: len(d["A"].shape) > 1 and len(d["B"].shape) > 1 and
          tasklet_matmul(d["A"].shape, d["B"].shape) is not None,
-         lambda node, d: gemm_build(node, d, False, False))
+         lambda node, d, uid: gemm_build(node, d, uid, False, False))
     make("Gemm", ["A", "B", "C"], ["Y"],
          lambda node, d: node.alpha == 1.0 and node.beta == 1.0 and node.transA == 0 and node.transB == 1 and
-         ("C" not in d or _prod(d["C"].shape) == d["B"].shape[0]),
-         lambda node, d: gemm_build(node, d, True, "C" in d))
+         ("C" not in d or (_prod(d["C"].shape) == d["B"].shape[0] and int(d["C"].shape[-1]) == d["B"].shape[0])),
+         lambda node, d, uid: gemm_build(node, d, uid, True, "C" in d))
 
-    def conv_build(node, d):
+    def conv_build(node, d, ws):
         pads = node.pads if node.pads is not None else [0, 0, 0, 0]
         strides = node.strides if node.strides is not None else [1, 1]
-        ws = "b200_ws_%s" % "".join(ch if ch.isalnum() else "_" for ch in node.label)
         fields, init, fini = conv_env_code(d["X"].shape, d["W"].shape, pads, strides, ws)
 
         class ConvEnv(B200Ops):
@@ -369,25 +388,26 @@ def _register():
          (node.pads is None or all(p == 0 for p in node.pads)) and node.auto_pad == "NOTSET" and
          node.ceil_mode == 0 and node.storage_order == 0 and
          (node.dilations is None or all(x == 1 for x in node.dilations)),
-         lambda node, d: (tasklet_maxpool(d["X"].shape, node.kernel_shape, node.strides, node.label), None))
+         lambda node, d, uid: (tasklet_maxpool(d["X"].shape, node.kernel_shape, node.strides, node.label), None))
     make("Softmax", ["input"], ["output"], lambda node, d: True,
-         lambda node, d: (tasklet_softmax(d["input"].shape, node.axis, False, node.label), None))
+         lambda node, d, uid: (tasklet_softmax(d["input"].shape, node.axis, False, node.label), None))
     make("LogSoftmax", ["input"], ["output"], lambda node, d: True,
-         lambda node, d: (tasklet_softmax(d["input"].shape, node.axis, True, node.label), None))
+         lambda node, d, uid: (tasklet_softmax(d["input"].shape, node.axis, True, node.label), None))
     make("ReduceMean", ["data"], ["reduced"],
          lambda node, d: tasklet_reduce_mean(d["data"].shape, node.axes) is not None,
-         lambda node, d: (tasklet_reduce_mean(d["data"].shape, node.axes, node.label), None))
+         lambda node, d, uid: (tasklet_reduce_mean(d["data"].shape, node.axes, node.label), None))
     for op in ("Add", "Sub", "Mul", "Div"):
-        make(op, ["A", "B"], ["C"], lambda node, d: True,
-             lambda node, d, op=op: (tasklet_binary(op, d["A"].shape, d["B"].shape), None))
-    make("Pow", ["X", "Y"], ["Z"], lambda node, d: True,
-         lambda node, d: (tasklet_binary("Pow", d["X"].shape, d["Y"].shape, ("_X", "_Y", "_Z")), None))
+        make(op, ["A", "B"], ["C"], lambda node, d, op=op: tasklet_binary(op, d["A"].shape, d["B"].shape) is not None,
+             lambda node, d, uid, op=op: (tasklet_binary(op, d["A"].shape, d["B"].shape), None))
+    make("Pow", ["X", "Y"], ["Z"],
+         lambda node, d: tasklet_binary("Pow", d["X"].shape, d["Y"].shape, ("_X", "_Y", "_Z")) is not None,
+         lambda node, d, uid: (tasklet_binary("Pow", d["X"].shape, d["Y"].shape, ("_X", "_Y", "_Z")), None))
     make("Sqrt", ["X"], ["Y"], lambda node, d: True,
-         lambda node, d: (tasklet_unary("Sqrt", d["X"].shape), None))
+         lambda node, d, uid: (tasklet_unary("Sqrt", d["X"].shape), None))
     make("Relu", ["X"], ["Y"], lambda node, d: True,
-         lambda node, d: (tasklet_unary("Relu", d["X"].shape), None))
+         lambda node, d, uid: (tasklet_unary("Relu", d["X"].shape), None))
     make("Erf", ["input"], ["output"], lambda node, d: True,
-         lambda node, d: (tasklet_unary("Erf", d["input"].shape, ("_input", "_output")), None))
+         lambda node, d, uid: (tasklet_unary("Erf", d["input"].shape, ("_input", "_output")), None))
     return _REGISTERED
 
 

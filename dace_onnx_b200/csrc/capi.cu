@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "contract.cuh"
+#include "tc_common.cuh"
 
 namespace b200 {
 
@@ -41,11 +42,36 @@ unsigned *device_status_ptr() {
   return cache[dev];
 }
 
+// Self-test of the bounded wait every tensor-core kernel uses: one CTA, one mbarrier that nothing ever arrives at,
+// no copies in flight, no TMEM. The wait gives up after `budget` cycles, records `code` in the status word and the
+// kernel returns normally.
+__global__ void __launch_bounds__(32)
+wait_expiry_selftest_kernel(unsigned *status, long long budget, unsigned code) {
+  __shared__ uint64_t bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    tc::mbar_init(tc::smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) tc::mbar_wait_budget(tc::smem_u32(&bar), 0, &s_abort, status, code, budget);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" B200_API int b200_version(void) { return 100; }
+
+extern "C" B200_API int b200_selftest_wait_expiry(void *stream, int64_t budget_cycles) {
+  if (budget_cycles < 1 || budget_cycles > 100000000LL)
+    return fail(B200_EINVAL, "selftest: the budget must be between 1 and 1e8 cycles");
+  unsigned *status = device_status_ptr();
+  if (!status) return fail(B200_ECUDA, "selftest: device status word unavailable");
+  wait_expiry_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (long long)budget_cycles, 0x8000u);
+  return check_launch("wait_expiry_selftest");
+}
 
 extern "C" B200_API const char *b200_last_error_string(void) { return g_error; }
 

@@ -25,8 +25,18 @@ gemm_simt_kernel(const float *__restrict__ A, const float *__restrict__ B, const
   const int64_t m0 = (int64_t)blockIdx.x * BM, n0 = (int64_t)blockIdx.y * BN;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
 
-  float acc[4][4] = {};
+  // Two-level sum: `acc` holds at most kFoldK products, then folds into `tot`. A single fp32 running sum over
+  // thousands of products loses ~sqrt(K) ulps to rounding; partial sums of 256 keep long-K results (K = 4096
+  // in the FFN) inside the fp32 parity tolerance.
+  constexpr int kFoldK = 256;
+  float acc[4][4] = {}, tot[4][4] = {};
   for (int64_t k0 = 0; k0 < d.K; k0 += BK) {
+    if (k0 && k0 % kFoldK == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { tot[i][j] += acc[i][j]; acc[i][j] = 0.f; }
+    }
     // A tile: BM x BK, K contiguous in memory.
     for (int i = tid; i < BM * BK; i += 256) {
       const int kk = i % BK, mm = i / BK;
@@ -65,7 +75,7 @@ gemm_simt_kernel(const float *__restrict__ A, const float *__restrict__ B, const
       const int64_t n = n0 + tx * 4 + j;
       if (n >= d.N) continue;
       const int64_t o = yoff + m * d.ldy + n;
-      Y[o] = apply_epilogue(d.epilogue, acc[i][j], bias ? bias[n] : 0.f, residual ? residual[o] : 0.f, d.scale);
+      Y[o] = apply_epilogue(d.epilogue, tot[i][j] + acc[i][j], bias ? bias[n] : 0.f, residual ? residual[o] : 0.f, d.scale);
     }
   }
 }

@@ -4,18 +4,24 @@
 // Rows of the GEMM are output pixels, N is the output-channel count (<= 64), K runs over
 // (kh, kw, 32-channel block). With N = 64 a tcgen05.mma is too small to keep the tensor pipe busy from a
 // single-CTA instruction stream, so two CTAs form a cluster and one instruction (cta_group::2, M = 256)
-// covers 256 pixels: 128 per CTA, four 8x8 blocks of output pixels per pair. Per CTA:
+// covers 256 pixels: 128 per CTA (a tile of 8 x 16 output pixels), two such tiles per pair. Per CTA:
 //   * the filter half this CTA contributes to the pair's B operand (N/2 channels x all of K, repacked and,
 //     in 3xTF32 mode, pre-split into hi / lo once by conv2d_prepare_filter) is loaded ONCE and stays in shared
 //     memory for the life of the persistent CTA -- it is not re-streamed per tile;
-//   * activations arrive NHWC through a ring of 16 KiB stages: for filter tap (kh, kw) and channel block cb
-//     the producer issues two 4-D TMA boxes {32 c, 8 w, 8 h, 1 n} at (32 cb, ow0 + kw - pad, oh0 + kh - pad, n);
-//     out-of-range coordinates are zero-filled by the TMA unit, which is the zero padding;
+//   * activations arrive NHWC through a ring of stages. A stage is the input slab under ONE filter column kw
+//     (and up to two 32-channel blocks): 8 pixels wide, 16 + KH - 1 pixels high, fetched by one 5-D TMA box
+//     {32 c, 8 w, 16 + KH - 1 h, 2 channel blocks, 1 n} at (0, ow0 + kw - pad, oh0 - pad, cb, n). Its rows are
+//     (h, w) pixels, 8 per image row, so the A operand of filter tap (kh, kw) is the 128 rows that start kh
+//     image rows = kh * 1024 bytes into the slab: the KH taps of a column share one load, and the input crosses
+//     the L2 -> shared-memory path KW times instead of KH * KW times (that path, not the tensor pipe, bounded a
+//     version with one load per tap). Out-of-range coordinates are zero-filled by the TMA unit, which is the
+//     zero padding. Two threads take turns issuing these loads (even / odd stages);
 //   * two threads of the even CTA issue the MMAs, each the k-steps of one half of every k-block into its own
 //     TMEM accumulator (one thread alone cannot issue N = 64 instructions as fast as the pipe retires them);
 //     the epilogue adds the two accumulators;
-//   * 3xTF32 mode: eight split warps turn each landed stage into hi = tf32(x) and lo = tf32(x - hi) halves in
-//     TMEM (the MMAs read A from TMEM, B_hi / B_lo from the resident filter) and run lo*hi + hi*lo + hi*hi;
+//   * 3xTF32 mode: eight split warps (two groups on alternate k-blocks) turn the landed rows into
+//     hi = tf32(x) and lo = tf32(x - hi) halves in TMEM (the MMAs read A from TMEM, B_hi / B_lo from the
+//     resident filter) and run lo*hi + hi*lo + hi*hi;
 //     accumulation is cut into chunks whose partial sums the epilogue adds in registers with round-to-nearest
 //     (the tensor core adds into its accumulator with round-toward-zero);
 //   * the epilogue applies bias / ReLU and writes either NHWC (each thread 128 contiguous bytes of its pixel:
@@ -33,7 +39,8 @@ namespace b200 {
 using namespace tc;
 namespace {
 
-constexpr int BM = 128;                     // output pixels per CTA and tile (two 8x8 blocks)
+constexpr int BM = 128;                     // output pixels per CTA and tile: 8 wide x 16 high
+constexpr int TW = 8, TH = 16;
 constexpr int BK = 32;                      // channels per k-block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;
 constexpr int A_STAGE_BYTES = BM * BK * 4;  // 16 KiB
@@ -45,12 +52,16 @@ constexpr int kBarrierBytes = 512;
 constexpr int kMaxDynamicSmem = 227 * 1024 - 1024;  // the rest of the 227 KiB is the kernel's static shared memory
 
 struct ConvPairParams {
-  int KW, pad_h, pad_w;
+  int KH, KW, pad_h, pad_w;
   int OH, OW;
-  int blocks_w, blocks_per_img;
+  int slab_bytes;              // one channel block of a stage: (16 + KH - 1) image rows x 8 pixels x 128 bytes
+  int tiles_w, tiles_per_img;  // 8 x 16 pixel tiles per row of tiles / per image
   int cblocks, num_kb;
-  int64_t total_blocks;  // images * blocks_per_img
-  int64_t num_tiles;     // groups of four blocks
+  int kbs;                // 32-channel blocks per stage: 2, or 1 when the input has at most 32 channels
+  int groups;             // stages per filter column
+  int stages_per_tile;    // KW * groups
+  int64_t total_tiles;    // images * tiles_per_img
+  int64_t num_tiles;      // pairs of tiles
   int bn;                // output channels rounded up to a multiple of 16 (the instruction's N)
   int M;                 // output channels
   int stages;
@@ -86,8 +97,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int b_bytes = p.num_kb * p.b_kb_bytes;  // resident filter, a multiple of 1024
+  const int stage_bytes = p.kbs * p.slab_bytes;
   uint8_t *stages = smem + b_bytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(stages + (size_t)p.stages * A_STAGE_BYTES);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(stages + (size_t)p.stages * stage_bytes);
   // full[8] empty[8] split[4] slotfree[4] tfull[4] tempty[4] bfull
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
@@ -115,7 +127,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       mbar_init(bar_empty + 8 * s, SPLIT3 ? C::kSplitWarps : 2);
     }
     for (int t = 0; t < kSlots; ++t) {
-      mbar_init(bar_split + 8 * t, 2 * 8);  // one arrival per split warp of both CTAs
+      mbar_init(bar_split + 8 * t, 2 * 4);  // one arrival per split warp of one group, both CTAs
       mbar_init(bar_slotfree + 8 * t, 2);   // both issuing threads' commits
     }
     for (int a = 0; a < 4; ++a) {
@@ -137,67 +149,59 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const uint32_t tmem_base = s_tmem_base;
   volatile int *abort_flag = &s_abort;
 
-  if (warp == 0) {
-    // ------------------------------- TMA producer (both CTAs) -------------------------------
+  if (warp == 0 || warp == 3) {
+    // ------------------------------- TMA producers (both CTAs) -------------------------------
+    // Two threads per CTA: producer j (warp 0: j = 0, warp 3: j = 1) loads the stages whose running number
+    // is congruent to j modulo 2. A stage is one filter column and p.kbs channel blocks, one TMA instruction.
     if (lane == 0) {
-      // The filter half of this CTA, once. The even CTA's barrier counts the bytes of both CTAs (the issuing
-      // threads live there): it posts the expectation, the partner's loads complete on it remotely.
-      const uint32_t bfull = rank == 0 ? bar_bfull : map_to_cta(bar_bfull, 0);
-      if (rank == 0) mbar_expect_tx(bar_bfull, 2u * (uint32_t)b_bytes);
-      const int half_rows = p.bn / 2;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
-        const uint32_t dst = smem_base + (uint32_t)(kb * p.b_kb_bytes);
-        if (rank == 0) {
-          tma_load_4d(dst, &map_w, bfull, kb * BK, 0, 0, 0);
-          if (SPLIT3) tma_load_4d(dst + half_rows * 128, &map_wlo, bfull, kb * BK, 0, 0, 0);
-        } else {
-          tma_load_4d_pair(dst, &map_w, bfull, kb * BK, half_rows, 0, 0);
-          if (SPLIT3) tma_load_4d_pair(dst + half_rows * 128, &map_wlo, bfull, kb * BK, half_rows, 0, 0);
+      const int j = warp == 0 ? 0 : 1;
+      if (j == 0) {
+        // The filter half of this CTA, once. The even CTA's barrier counts the bytes of both CTAs (the issuing
+        // threads live there): it posts the expectation, the partner's loads complete on it remotely.
+        const uint32_t bfull = rank == 0 ? bar_bfull : map_to_cta(bar_bfull, 0);
+        if (rank == 0) mbar_expect_tx(bar_bfull, 2u * (uint32_t)b_bytes);
+        const int half_rows = p.bn / 2;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          const uint32_t dst = smem_base + (uint32_t)(kb * p.b_kb_bytes);
+          if (rank == 0) {
+            tma_load_4d(dst, &map_w, bfull, kb * BK, 0, 0, 0);
+            if (SPLIT3) tma_load_4d(dst + half_rows * 128, &map_wlo, bfull, kb * BK, 0, 0, 0);
+          } else {
+            tma_load_4d_pair(dst, &map_w, bfull, kb * BK, half_rows, 0, 0);
+            if (SPLIT3) tma_load_4d_pair(dst + half_rows * 128, &map_wlo, bfull, kb * BK, half_rows, 0, 0);
+          }
         }
       }
-      int s = 0;
-      uint32_t ph = 0;
       bool ok = true;
       const uint32_t full_pair0 = map_to_cta(bar_full, 0);
+      int64_t g = 0;  // running stage number of this CTA
       for (int64_t tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
-        // the two 8x8 output blocks of this CTA, decomposed once per tile
-        int cv_img[2], cv_x[2], cv_y[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int64_t blk = 4 * tile + 2 * (int64_t)rank + h;
-          cv_img[h] = (int)(blk / p.blocks_per_img);
-          const int rem = (int)(blk - (int64_t)cv_img[h] * p.blocks_per_img);
-          const int by = rem / p.blocks_w;
-          cv_y[h] = by * 8 - p.pad_h;
-          cv_x[h] = (rem - by * p.blocks_w) * 8 - p.pad_w;
-        }
-        int kh = 0, kw = 0, cb = 0;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
-          const uint32_t dst = stage_base + (uint32_t)s * A_STAGE_BYTES;
-          uint32_t full;
-          if (SPLIT3) {
-            // each CTA's split warps consume its own stage: local barrier, local bytes
-            full = bar_full + 8 * s;
-            mbar_expect_tx(full, A_STAGE_BYTES);
-          } else {
-            // the issuing threads (even CTA) consume both CTAs' stages: one barrier there for both
-            full = rank == 0 ? bar_full + 8 * s : full_pair0 + 8 * s;
-            if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * A_STAGE_BYTES);
+        // this CTA's 8 x 16 tile of output pixels, decomposed once per tile
+        const int64_t ct = 2 * tile + (int64_t)rank;
+        const int img = (int)(ct / p.tiles_per_img);
+        const int rem = (int)(ct - (int64_t)img * p.tiles_per_img);
+        const int ty = rem / p.tiles_w;
+        const int y0 = ty * TH - p.pad_h, x0 = (rem - ty * p.tiles_w) * TW - p.pad_w;
+        int kw = 0, grp = 0;
+        for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
+          if ((g & 1) == j) {
+            const int s = (int)(g % kStages);
+            const uint32_t ph = (uint32_t)((g / kStages) & 1);
+            if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
+            const uint32_t dst = stage_base + (uint32_t)(s * stage_bytes);
+            if (SPLIT3) {
+              // each CTA's split warps consume its own stage: local barrier, local bytes
+              mbar_expect_tx(bar_full + 8 * s, (uint32_t)stage_bytes);
+              tma_load_5d(dst, &map_x, bar_full + 8 * s, 0, x0 + kw, y0, grp * 2, img);
+            } else if (rank == 0) {
+              // the issuing threads (even CTA) consume both CTAs' stages: one barrier there for both
+              mbar_expect_tx(bar_full + 8 * s, 2u * (uint32_t)stage_bytes);
+              tma_load_5d(dst, &map_x, bar_full + 8 * s, 0, x0 + kw, y0, grp * 2, img);
+            } else {
+              tma_load_5d_pair(dst, &map_x, full_pair0 + 8 * s, 0, x0 + kw, y0, grp * 2, img);
+            }
           }
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (SPLIT3 || rank == 0)
-              tma_load_4d(dst + h * (A_STAGE_BYTES / 2), &map_x, full, cb * BK, cv_x[h] + kw, cv_y[h] + kh, cv_img[h]);
-            else
-              tma_load_4d_pair(dst + h * (A_STAGE_BYTES / 2), &map_x, full, cb * BK, cv_x[h] + kw, cv_y[h] + kh,
-                               cv_img[h]);
-          }
-          if (++cb == p.cblocks) {
-            cb = 0;
-            if (++kw == p.KW) { kw = 0; ++kh; }
-          }
-          if (++s == kStages) { s = 0; ph ^= 1; }
+          if (++grp == p.groups) { grp = 0; ++kw; }
         }
       }
     }
@@ -212,47 +216,72 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       const uint64_t b_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128) + (uint32_t)(2 * i) * kStep;
       const uint32_t b_kb16 = (uint32_t)p.b_kb_bytes >> 4;
       const uint32_t b_lo16 = (uint32_t)(p.bn / 2 * 128) >> 4;
+      const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
       bool ok = mbar_wait(bar_bfull, 0, abort_flag, p.status, 64u);
       tc_fence_after();
       int s = 0, slot = 0, buf = 0;
       uint32_t ph = 0, slot_ph = 0, buf_ph = 0;
-      const int chunk = SPLIT3 ? kChunkKb : p.num_kb;
+      const uint32_t slab16 = (uint32_t)p.slab_bytes >> 4;
       for (int64_t tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
-        for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += chunk) {
-          const int a = 2 * i + buf;
-          if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(a * kAccCols);
-          const int kb_end = kb0 + chunk < p.num_kb ? kb0 + chunk : p.num_kb;
-          for (int kb = kb0; kb < kb_end; ++kb) {
-            const uint64_t b_d = b_desc0 + (uint32_t)kb * b_kb16;
-            const uint32_t first = kb > kb0 ? 1u : 0u;
-            if (SPLIT3) {
-              if (!(ok = mbar_wait(bar_split + 8 * slot, slot_ph, abort_flag, p.status, 4u))) break;
-              tc_fence_after();
-              const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)slot * 64 + (uint32_t)(2 * i) * UMMA_K;
+        // K order of a tile: filter column kw, channel-block group, channel block q, filter row kh -- the order
+        // in which the slabs arrive. `n` counts the tile's k-blocks; 3xTF32 starts a new accumulator every
+        // kChunkKb of them.
+        int n = 0, kw = 0, grp = 0;
+        int a = 2 * i + buf;
+        uint32_t d_tmem = tmem_base + (uint32_t)(a * kAccCols);
+        if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
+        tc_fence_after();
+        for (int st = 0; st < p.stages_per_tile && ok; ++st) {
+          const int nkb = p.cblocks - grp * 2 < p.kbs ? p.cblocks - grp * 2 : p.kbs;  // valid channel blocks here
+          if (!SPLIT3) {
+            if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 4u))) break;
+            tc_fence_after();
+          }
+          for (int q = 0; q < nkb && ok; ++q) {
+            for (int kh = 0; kh < p.KH; ++kh, ++n) {
+              const int kb = (kh * p.KW + kw) * p.cblocks + grp * 2 + q;  // this k-block's slice of the filter
+              const uint64_t b_d = b_desc0 + (uint32_t)kb * b_kb16;
+              if (SPLIT3) {
+                if (n && n % kChunkKb == 0) {
+                  // chunk boundary: publish this accumulator, continue in the other one
+                  umma_commit_pair_both(bar_tfull + 8 * a, 3);
+                  if (++buf == 2) { buf = 0; buf_ph ^= 1; }
+                  a = 2 * i + buf;
+                  d_tmem = tmem_base + (uint32_t)(a * kAccCols);
+                  if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
+                  tc_fence_after();
+                }
+                const uint32_t first = n % kChunkKb ? 1u : 0u;
+                if (!(ok = mbar_wait(bar_split + 8 * slot, slot_ph, abort_flag, p.status, 4u))) break;
+                tc_fence_after();
+                const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)slot * 64 + (uint32_t)(2 * i) * UMMA_K;
 #pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K + 32, b_d + j * kStep, idesc, j > 0 ? 1u : first);  // lo * hi
-                umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + b_lo16 + j * kStep, idesc, 1u);              // hi * lo
-                umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + j * kStep, idesc, 1u);                       // hi * hi
+                for (int j = 0; j < 2; ++j) {
+                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K + 32, b_d + j * kStep, idesc, j > 0 ? 1u : first);  // lo * hi
+                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + b_lo16 + j * kStep, idesc, 1u);              // hi * lo
+                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + j * kStep, idesc, 1u);                       // hi * hi
+                }
+                umma_commit_pair_both(bar_slotfree + 8 * slot, 3);
+                if (++slot == kSlots) { slot = 0; slot_ph ^= 1; }
+              } else {
+                // rows [8 kh, 8 kh + 128) of channel block q of the slab: kh image rows = kh * 1024 bytes down
+                const uint64_t a_d = a_desc0 + (uint32_t)s * stage16 + (uint32_t)q * slab16 + (uint32_t)kh * (1024 >> 4);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                  umma_tf32_pair(d_tmem, a_d + j * kStep, b_d + j * kStep, idesc, (j > 0 || n > 0) ? 1u : 0u);
               }
-              umma_commit_pair_both(bar_slotfree + 8 * slot, 3);
-              if (++slot == kSlots) { slot = 0; slot_ph ^= 1; }
-            } else {
-              if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 4u))) break;
-              tc_fence_after();
-              const uint64_t a_d = a_desc0 + (uint32_t)s * (A_STAGE_BYTES >> 4);
-#pragma unroll
-              for (int j = 0; j < 2; ++j) umma_tf32_pair(d_tmem, a_d + j * kStep, b_d + j * kStep, idesc, j > 0 ? 1u : first);
-              umma_commit_pair_both(bar_empty + 8 * s, 3);
-              if (++s == kStages) { s = 0; ph ^= 1; }
             }
           }
           if (!ok) break;
-          umma_commit_pair_both(bar_tfull + 8 * a, 3);
-          if (++buf == 2) { buf = 0; buf_ph ^= 1; }
+          if (!SPLIT3) {
+            umma_commit_pair_both(bar_empty + 8 * s, 3);
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
+          if (++grp == p.groups) { grp = 0; ++kw; }
         }
+        if (!ok) break;
+        umma_commit_pair_both(bar_tfull + 8 * a, 3);
+        if (++buf == 2) { buf = 0; buf_ph ^= 1; }
       }
     }
   } else if (warp >= C::kEpilogueWarp0 && warp < C::kSplitWarp0) {
@@ -298,13 +327,13 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (++buf == 2) { buf = 0; buf_ph ^= 1; }
       }
       if (!ok) break;
-      // this thread's output pixel
-      const int64_t blk = 4 * tile + 2 * (int64_t)rank + (row >> 6);
-      const int img = (int)(blk / p.blocks_per_img);
-      const int rem = (int)(blk - (int64_t)img * p.blocks_per_img);
-      const int by = rem / p.blocks_w, bx = rem - by * p.blocks_w;
-      const int oh = by * 8 + ((row & 63) >> 3), ow = bx * 8 + (row & 7);
-      if (blk < p.total_blocks && oh < p.OH && ow < p.OW && col0 < p.M) {
+      // this thread's output pixel: row r of the tile is pixel (r / 8, r % 8)
+      const int64_t ct = 2 * tile + (int64_t)rank;
+      const int img = (int)(ct / p.tiles_per_img);
+      const int rem = (int)(ct - (int64_t)img * p.tiles_per_img);
+      const int ty = rem / p.tiles_w;
+      const int oh = ty * TH + (row >> 3), ow = (rem - ty * p.tiles_w) * TW + (row & 7);
+      if (ct < p.total_tiles && oh < p.OH && ow < p.OW && col0 < p.M) {
         const int ncols = p.M - col0 < 32 ? p.M - col0 : 32;
         if (p.epilogue != B200_EPI_NONE) {
 #pragma unroll
@@ -339,45 +368,68 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
   } else if (SPLIT3 && warp >= C::kSplitWarp0) {
     // ------------------------------- split warps: A -> hi / lo halves in TMEM -------------------------------
+    // Two groups of four warps (one warp per TMEM lane quarter, one pixel row per thread). Group g converts the
+    // k-blocks whose running number has parity g, so two k-blocks are in conversion at any time: one warp's
+    // load -> convert -> wait for the slot -> tcgen05.st -> publish chain is longer than the MMAs of a k-block.
     const int quarter = warp & 3;
-    const int colhalf = (warp - C::kSplitWarp0) >> 2;  // which 16 of the row's 32 values this warp splits
+    const int group = (warp - C::kSplitWarp0) >> 2;
     const int row = quarter * 32 + lane;
-    const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kSlotCol0 + colhalf * 16;
+    const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kSlotCol0;
     const uint32_t split0 = rank == 0 ? bar_split : map_to_cta(bar_split, 0);
-    int s = 0, slot = 0;
-    uint32_t ph = 0, slot_ph = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    int64_t n = 0;  // running k-block number of this CTA: slot n % kSlots, converted by group n % 2
     bool ok = true;
     for (int64_t tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      int grp = 0;
+      for (int st = 0; st < p.stages_per_tile && ok; ++st) {
         if (!(ok = mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 16u))) break;
-        const float4 *arow = reinterpret_cast<const float4 *>(stages + (size_t)s * A_STAGE_BYTES + row * 128);
-        uint32_t hi[16], lo[16];
+        const int nkb = p.cblocks - grp * 2 < p.kbs ? p.cblocks - grp * 2 : p.kbs;
+        for (int q = 0; q < nkb && ok; ++q) {
+          for (int kh = 0; kh < p.KH; ++kh, ++n) {
+            if ((int)(n & 1) != group) continue;
+            const int slot = (int)(n & (kSlots - 1));
+            const uint32_t slot_ph = (uint32_t)((n / kSlots) & 1);
+            // this thread's pixel under filter row kh: slab row 8 kh + row of channel block q
+            const int srow = kh * 8 + row;
+            const float4 *arow = reinterpret_cast<const float4 *>(stages + (size_t)s * stage_bytes +
+                                                                  (size_t)q * p.slab_bytes + (size_t)srow * 128);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float4 x = arow[(colhalf * 4 + c) ^ (row & 7)];
-          const float h0 = to_tf32_rna(x.x), h1 = to_tf32_rna(x.y), h2 = to_tf32_rna(x.z), h3 = to_tf32_rna(x.w);
-          hi[4 * c + 0] = __float_as_uint(h0); hi[4 * c + 1] = __float_as_uint(h1);
-          hi[4 * c + 2] = __float_as_uint(h2); hi[4 * c + 3] = __float_as_uint(h3);
-          lo[4 * c + 0] = __float_as_uint(to_tf32_rna(x.x - h0)); lo[4 * c + 1] = __float_as_uint(to_tf32_rna(x.y - h1));
-          lo[4 * c + 2] = __float_as_uint(to_tf32_rna(x.z - h2)); lo[4 * c + 3] = __float_as_uint(to_tf32_rna(x.w - h3));
+            for (int half = 0; half < 2; ++half) {
+              uint32_t hi[16], lo[16];
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const float4 x = arow[(half * 4 + c) ^ (srow & 7)];
+                const float h0 = to_tf32_rna(x.x), h1 = to_tf32_rna(x.y), h2 = to_tf32_rna(x.z), h3 = to_tf32_rna(x.w);
+                hi[4 * c + 0] = __float_as_uint(h0); hi[4 * c + 1] = __float_as_uint(h1);
+                hi[4 * c + 2] = __float_as_uint(h2); hi[4 * c + 3] = __float_as_uint(h3);
+                lo[4 * c + 0] = __float_as_uint(to_tf32_rna(x.x - h0)); lo[4 * c + 1] = __float_as_uint(to_tf32_rna(x.y - h1));
+                lo[4 * c + 2] = __float_as_uint(to_tf32_rna(x.z - h2)); lo[4 * c + 3] = __float_as_uint(to_tf32_rna(x.w - h3));
+              }
+              if (half == 0) {
+                // the slot was last read by the MMAs of the k-block kSlots before this one
+                if (!(ok = mbar_wait(bar_slotfree + 8 * slot, slot_ph ^ 1, abort_flag, p.status, 32u))) break;
+                tc_fence_after();
+              }
+              tmem_st16(a_lane + (uint32_t)slot * 64 + half * 16, hi);
+              tmem_st16(a_lane + (uint32_t)slot * 64 + 32 + half * 16, lo);
+            }
+            if (!ok) break;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if (rank == 0) mbar_arrive(bar_split + 8 * slot);
+              else mbar_arrive_cluster_relaxed(split0 + 8 * slot);
+            }
+          }
         }
-        // the stage's values are in registers: hand the shared-memory stage back to the producer
+        if (!ok) break;
+        // this warp has read all it needs of the stage: hand it back to its producer
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-        // the slot was last read by the MMAs of the k-block kSlots before this one
-        if (!(ok = mbar_wait(bar_slotfree + 8 * slot, slot_ph ^ 1, abort_flag, p.status, 32u))) break;
-        tc_fence_after();
-        tmem_st16(a_lane + (uint32_t)slot * 64, hi);
-        tmem_st16(a_lane + (uint32_t)slot * 64 + 32, lo);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (rank == 0) mbar_arrive(bar_split + 8 * slot);
-          else mbar_arrive_cluster_relaxed(split0 + 8 * slot);
-        }
         if (++s == kStages) { s = 0; ph ^= 1; }
-        if (++slot == kSlots) { slot = 0; slot_ph ^= 1; }
+        if (++grp == p.groups) grp = 0;
       }
     }
   }
@@ -422,27 +474,36 @@ conv_prepare_filter_kernel(const float *__restrict__ w, float *__restrict__ raw,
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct PairPlan {
-  int bn, stages, b_kb_bytes, num_kb;
+  int bn, stages, b_kb_bytes, num_kb, kbs, groups;
   size_t smem;
 };
 
 // Does the resident-filter pair kernel cover this convolution, and with which geometry?
 bool pair_plan(const b200_conv_desc &d, PairPlan *out) {
   if (d.M < 1 || d.M > 64) return false;
+  // the channel axis is described to TMA as {32 within a block, block}: whole blocks, or a single partial one
+  if (d.C > 32 && d.C % 32 != 0) return false;
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   PairPlan pl;
   pl.bn = (int)((d.M + 15) / 16 * 16);
-  const int64_t num_kb = d.KH * d.KW * ((d.C + 31) / 32);
+  const int64_t cblocks = (d.C + 31) / 32;
+  const int64_t num_kb = d.KH * d.KW * cblocks;
+  pl.kbs = cblocks > 1 ? 2 : 1;
+  pl.groups = (int)((cblocks + pl.kbs - 1) / pl.kbs);
   pl.b_kb_bytes = (split3 ? 2 : 1) * (pl.bn / 2) * 128;
   const int64_t b_bytes = num_kb * pl.b_kb_bytes;
+  const int64_t slab_rows = TH + d.KH - 1;  // image rows of a slab; 8 pixels = 1024 bytes each
+  if (slab_rows > 256) return false;        // TMA box extent
+  const int64_t stage_bytes = (int64_t)pl.kbs * slab_rows * 1024;
   const int64_t budget = kMaxDynamicSmem - 1024 /*alignment slack*/ - kBarrierBytes;
-  if (b_bytes > budget - 3 * A_STAGE_BYTES) return false;
-  int64_t stages = (budget - b_bytes) / A_STAGE_BYTES;
+  if (b_bytes > budget - 2 * stage_bytes) return false;
+  int64_t stages = (budget - b_bytes) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
   if (2 * b_bytes > 1000000) return false;  // one mbarrier transaction count holds both CTAs' filter bytes
+  if (d.KW * pl.groups > 0x7fffffffLL) return false;
   pl.stages = (int)stages;
   pl.num_kb = (int)num_kb;
-  pl.smem = (size_t)(b_bytes + stages * A_STAGE_BYTES + 1024 + kBarrierBytes);
+  pl.smem = (size_t)(b_bytes + stages * stage_bytes + 1024 + kBarrierBytes);
   *out = pl;
   return true;
 }
@@ -572,9 +633,12 @@ int conv2d_run(cudaStream_t st, const b200_conv_desc &d, int flags, const float 
   const float *w_lo = split3 ? reinterpret_cast<const float *>(static_cast<const char *>(filter) + 2 * one) : w_raw;
   CUtensorMap mx, mw, mwlo;
   {
-    uint64_t dims[4] = {(uint64_t)d.C, (uint64_t)d.W, (uint64_t)d.H, (uint64_t)d.N};
-    uint64_t str[3] = {(uint64_t)d.C * 4, (uint64_t)d.W * d.C * 4, (uint64_t)d.H * d.W * d.C * 4};
-    if (int rc = encode_map(&mx, xt, dims, str, BK, 8, CU_TENSOR_MAP_SWIZZLE_128B, 8)) return rc;
+    // NHWC input seen as {32 channels of a block, W, H, channel block, N}; one box = the slab of one filter column
+    const uint64_t cblocks = (uint64_t)((d.C + 31) / 32);
+    uint64_t dims[5] = {(uint64_t)(d.C < 32 ? d.C : 32), (uint64_t)d.W, (uint64_t)d.H, cblocks, (uint64_t)d.N};
+    uint64_t str[4] = {(uint64_t)d.C * 4, (uint64_t)d.W * d.C * 4, 128, (uint64_t)d.H * d.W * d.C * 4};
+    uint32_t box[5] = {BK, TW, (uint32_t)(TH + d.KH - 1), (uint32_t)pl.kbs, 1};
+    if (int rc = encode_map5(&mx, xt, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   }
   {
     uint64_t dims[4] = {(uint64_t)taps * Cp, (uint64_t)d.M, 1, 1};
@@ -583,17 +647,22 @@ int conv2d_run(cudaStream_t st, const b200_conv_desc &d, int flags, const float 
     if (int rc = encode_map(&mwlo, w_lo, dims, str, BK, (uint32_t)(pl.bn / 2), CU_TENSOR_MAP_SWIZZLE_128B)) return rc;
   }
   ConvPairParams p{};
+  p.KH = (int)d.KH;
   p.KW = (int)d.KW;
   p.pad_h = (int)d.pad_h;
   p.pad_w = (int)d.pad_w;
   p.OH = (int)OH;
   p.OW = (int)OW;
-  p.blocks_w = (int)((OW + 7) / 8);
-  p.blocks_per_img = p.blocks_w * (int)((OH + 7) / 8);
+  p.slab_bytes = (int)((TH + d.KH - 1) * 1024);
+  p.tiles_w = (int)((OW + TW - 1) / TW);
+  p.tiles_per_img = p.tiles_w * (int)((OH + TH - 1) / TH);
   p.cblocks = Cp / 32;
   p.num_kb = pl.num_kb;
-  p.total_blocks = d.N * p.blocks_per_img;
-  p.num_tiles = (p.total_blocks + 3) / 4;
+  p.kbs = pl.kbs;
+  p.groups = pl.groups;
+  p.stages_per_tile = (int)d.KW * pl.groups;
+  p.total_tiles = d.N * p.tiles_per_img;
+  p.num_tiles = (p.total_tiles + 1) / 2;
   p.bn = pl.bn;
   p.M = (int)d.M;
   p.stages = pl.stages;
@@ -605,7 +674,7 @@ int conv2d_run(cudaStream_t st, const b200_conv_desc &d, int flags, const float 
   p.Y = Y;
   p.status = device_status_ptr();
   if (!p.status) return fail(B200_ECUDA, "conv(pair): device status word unavailable");
-  if (4 * p.num_tiles > 0x7fffffff00LL) return fail(B200_EUNSUPPORTED, "conv: too many output tiles");
+  if (p.total_tiles > 0x7fffffff00LL) return fail(B200_EUNSUPPORTED, "conv: too many output tiles");
   return split3 ? launch_pair_conv<true>(st, pl, mx, mw, mwlo, p) : launch_pair_conv<false>(st, pl, mx, mw, mwlo, p);
 }
 

@@ -1209,6 +1209,25 @@ int tc::encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], 
 }
 
 
+int tc::encode_map5(CUtensorMap *map, const float *base, const uint64_t dims[5], const uint64_t strides_bytes[4],
+                    const uint32_t box[5], CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[5] = {dims[0], dims[1], dims[2], dims[3], dims[4]};
+  cuuint64_t gstr[4] = {strides_bytes[0], strides_bytes[1], strides_bytes[2], strides_bytes[3]};
+  cuuint32_t bx[5] = {box[0], box[1], box[2], box[3], box[4]};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(base), gdim, gstr, bx, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200_ECUDA, "cuTensorMapEncodeTiled (rank 5) failed (%d): dims {%llu,%llu,%llu,%llu,%llu} box {%u,%u,%u,%u,%u}",
+                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                (unsigned long long)dims[3], (unsigned long long)dims[4], box[0], box[1], box[2], box[3], box[4]);
+  return B200_OK;
+}
+
+
 bool gemm_tc_supported(const b200_gemm_desc &d, const float *A, const float *B, const float *Y) {
   auto ok4 = [](int64_t v) { return v % 4 == 0; };
   if (d.M < 1 || d.N < 1 || d.K < 1) return false;

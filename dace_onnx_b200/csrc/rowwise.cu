@@ -8,9 +8,9 @@
 // order of the reference's pure expansions (max, subtract, exp, sum, divide; mean, centred
 // second moment, sqrt, divide) with IEEE expf/logf/sqrtf and true division (no fast-math).
 #include <math.h>
-#include <stdlib.h>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace b200 {
 namespace {
@@ -231,36 +231,82 @@ layernorm_warp_vec_kernel(const float *__restrict__ x, const float *__restrict__
   }
 }
 
-// The same arithmetic as a persistent kernel: each warp walks rows with a grid stride and issues the 128-bit
-// loads of its NEXT row before it reduces and stores the current one, so every warp keeps a full row of loads in
-// flight through its reduction and store phases (the one-row-per-warp form above has nothing in flight then, and
-// pays a CTA launch per eight rows). Grid = a multiple of the SM count.
+// The same arithmetic with the rows staged in shared memory by the bulk-copy engine. One persistent CTA per SM,
+// 16 warps; every warp owns a ring of `depth` row buffers in shared memory and keeps `depth` rows of loads in
+// flight with cp.async.bulk (a row is one contiguous block of global memory, so one instruction by one lane moves
+// it and signals an mbarrier): ~190 KiB in flight per SM regardless of what the warps are doing, where register
+// staging keeps only what the resident warps have issued. gamma / beta live in registers for the whole kernel.
+constexpr int kBulkWarps = 16;
+
+__device__ __forceinline__ void bulk_load_row(uint32_t dst, const float *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 template <int VPT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
-layernorm_warp_pipe_kernel(const float *__restrict__ x, const float *__restrict__ gamma,
-                           const float *__restrict__ beta, float *__restrict__ y, int64_t rows, int len, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerCta;
-  int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  const int nvec = len >> 2;
-  const float inv_len = 1.0f / (float)len;
-  float4 v[VPT], nx[VPT];
-  if (row < rows) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i)
-      if (lane + 32 * i < nvec) v[i] = ld_stream4(x + row * len + 4 * (lane + 32 * i));
+__global__ void __launch_bounds__(kBulkWarps * 32, 1)
+layernorm_bulk_kernel(const float *__restrict__ x, const float *__restrict__ gamma, const float *__restrict__ beta,
+                      float *__restrict__ y, int64_t rows, int len, float eps, int depth, unsigned *status) {
+  extern __shared__ __align__(128) uint8_t ln_smem[];
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row_bytes = (uint32_t)len * 4;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(ln_smem + (size_t)kBulkWarps * depth * row_bytes);
+  const uint32_t my_bar = tc::smem_u32(bars + warp * depth);
+  const uint32_t my_buf = tc::smem_u32(ln_smem + (size_t)warp * depth * row_bytes);
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kBulkWarps * depth; ++i) tc::mbar_init(tc::smem_u32(bars + i), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (; row < rows; row += nwarps) {
-    const int64_t next = row + nwarps;
-    if (next < rows) {
+  __syncthreads();
+  volatile int *abort_flag = &s_abort;
+  const int64_t nwarps = (int64_t)gridDim.x * kBulkWarps;
+  const int64_t first = (int64_t)blockIdx.x * kBulkWarps + warp;
+  const int nvec = len >> 2;
+
+  float4 g[VPT], b[VPT];
 #pragma unroll
-      for (int i = 0; i < VPT; ++i)
-        if (lane + 32 * i < nvec) nx[i] = ld_stream4(x + next * len + 4 * (lane + 32 * i));
+  for (int i = 0; i < VPT; ++i) {
+    const int c = lane + 32 * i;
+    g[i] = (gamma && c < nvec) ? __ldg(reinterpret_cast<const float4 *>(gamma + 4 * c)) : make_float4(1.f, 1.f, 1.f, 1.f);
+    b[i] = (beta && c < nvec) ? __ldg(reinterpret_cast<const float4 *>(beta + 4 * c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (lane == 0) {
+    for (int j = 0; j < depth; ++j) {
+      const int64_t r = first + j * nwarps;
+      if (r < rows) {
+        tc::mbar_expect_tx(my_bar + 8 * j, row_bytes);
+        bulk_load_row(my_buf + j * row_bytes, x + r * len, row_bytes, my_bar + 8 * j);
+      }
     }
+  }
+  int slot = 0;
+  uint32_t ph = 0;
+  for (int64_t row = first; row < rows; row += nwarps) {
+    if (!tc::mbar_wait(my_bar + 8 * slot, ph, abort_flag, status, 128u)) break;
+    const float4 *src = reinterpret_cast<const float4 *>(ln_smem + ((size_t)warp * depth + slot) * row_bytes);
+    float4 v[VPT];
     float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i)
-      if (lane + 32 * i < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    for (int i = 0; i < VPT; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        v[i] = src[c];
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+    }
+    // the row is in registers: refill this buffer with the row `depth` iterations ahead
+    __syncwarp();
+    if (lane == 0) {
+      const int64_t next = row + (int64_t)depth * nwarps;
+      if (next < rows) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc::mbar_expect_tx(my_bar + 8 * slot, row_bytes);
+        bulk_load_row(my_buf + slot * row_bytes, x + next * len, row_bytes, my_bar + 8 * slot);
+      }
+    }
     const float mean = warp_sum(s) / (float)len;  // ReduceMean
     float q = 0.f;
 #pragma unroll
@@ -271,7 +317,7 @@ layernorm_warp_pipe_kernel(const float *__restrict__ x, const float *__restrict_
       }
     }
     const float var = warp_sum(q) / (float)len;  // ReduceMean
-    const float inv = 1.0f / sqrtf(var + eps);   // Add eps, Sqrt, and Div as one reciprocal per row
+    const float inv = 1.0f / sqrtf(var + eps);   // Add eps, Sqrt; Div as one reciprocal per row (see above)
     float *yr = y + row * len;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -279,20 +325,18 @@ layernorm_warp_pipe_kernel(const float *__restrict__ x, const float *__restrict_
       if (c < nvec) {
         float4 o;
         o.x = v[i].x * inv; o.y = v[i].y * inv; o.z = v[i].z * inv; o.w = v[i].w * inv;
-        if (gamma) {
-          const float4 g = __ldg(reinterpret_cast<const float4 *>(gamma + 4 * c));
-          o.x *= g.x; o.y *= g.y; o.z *= g.z; o.w *= g.w;  // Mul
-        }
-        if (beta) {
-          const float4 b = __ldg(reinterpret_cast<const float4 *>(beta + 4 * c));
-          o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;  // Add
-        }
+        if (gamma) { o.x *= g[i].x; o.y *= g[i].y; o.z *= g[i].z; o.w *= g[i].w; }  // Mul
+        if (beta) { o.x += b[i].x; o.y += b[i].y; o.z += b[i].z; o.w += b[i].w; }    // Add
         st_stream4(yr + 4 * c, o);
       }
     }
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) v[i] = nx[i];
-    (void)inv_len;
+    if (++slot == depth) { slot = 0; ph ^= 1; }
+  }
+  // an aborting warp may still have copies in flight into this CTA's shared memory: give them time to land
+  __syncthreads();
+  if (s_abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
   }
 }
 
@@ -449,17 +493,28 @@ extern "C" B200_API int b200_layernorm_f32(void *stream, const float *x, const f
   if (!x || !y) return fail(B200_EINVAL, "layernorm: null pointer");
   const bool vec_ok = (len % 4 == 0) && aligned16(x) && aligned16(y) && (!gamma || aligned16(gamma)) &&
                       (!beta || aligned16(beta));
-  static const int variant = getenv("B200_LN_VARIANT") ? atoi(getenv("B200_LN_VARIANT")) : 0;
-  if (vec_ok && len <= 1024 && len > 256 && variant > 0 && rows >= 8 * kNumSMs) {
-    const unsigned grid = (unsigned)(kNumSMs * variant);
+  // Large tensors of BERT-width rows: the persistent bulk-copy kernel (measured inside the encoder step it sustains
+  // 0.85 of the HBM copy rate where the one-row-per-warp kernel reaches 0.78); small ones: one warp per row.
+  if (vec_ok && len <= 1024 && len >= 256 && rows >= 4 * kBulkWarps * kNumSMs) {
     const int nvec = (int)(len >> 2);
-#define B200_LN_PIPE(V)                                                                          \
-  layernorm_warp_pipe_kernel<V><<<grid, kWarpsPerCta * 32, 0, st>>>(x, gamma, beta, y, rows, (int)len, eps)
-    if (nvec <= 128) B200_LN_PIPE(4);
-    else if (nvec <= 192) B200_LN_PIPE(6);
-    else B200_LN_PIPE(8);
-#undef B200_LN_PIPE
-    return check_launch("layernorm_warp_pipe");
+    int depth = (int)((200 * 1024) / ((size_t)kBulkWarps * len * 4));
+    if (depth > 8) depth = 8;
+    const size_t smem = (size_t)kBulkWarps * depth * len * 4 + (size_t)kBulkWarps * depth * 8;
+    unsigned *status = device_status_ptr();
+    if (!status) return fail(B200_ECUDA, "layernorm: device status word unavailable");
+#define B200_LN_BULK(V)                                                                                              \
+  do {                                                                                                               \
+    if (cudaFuncSetAttribute(layernorm_bulk_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024) !=   \
+        cudaSuccess)                                                                                                 \
+      return fail(B200_ECUDA, "layernorm: cannot raise the dynamic shared memory limit");                           \
+    layernorm_bulk_kernel<V><<<kNumSMs, kBulkWarps * 32, smem, st>>>(x, gamma, beta, y, rows, (int)len, eps, depth,  \
+                                                                     status);                                        \
+  } while (0)
+    if (nvec <= 128) B200_LN_BULK(4);
+    else if (nvec <= 192) B200_LN_BULK(6);
+    else B200_LN_BULK(8);
+#undef B200_LN_BULK
+    return check_launch("layernorm_bulk");
   }
   if (vec_ok && len <= 2048) {
     const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);

@@ -39,21 +39,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait. Returns false when the CTA is aborting (budget exceeded here or in another role).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned *status, unsigned code) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                 unsigned *status, unsigned code, long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0xffu) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycleBudget) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         atomicOr(status, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          unsigned *status, unsigned code) {
+  return mbar_wait_budget(bar, parity, abort_flag, status, code, kWaitCycleBudget);
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
@@ -62,6 +66,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
       "%6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 
@@ -216,6 +229,14 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(ncols) : "memory");
 }
@@ -266,6 +287,9 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int n, bool b_mn_major) {
 // rank-4 fp32 tensor map: dims {d0 (contiguous), d1, d2, d3}, byte strides for d1..d3, zero OOB fill.
 int encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
                uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, uint32_t box2 = 1);
+// rank-5 fp32 tensor map with an explicit box
+int encode_map5(CUtensorMap *map, const float *base, const uint64_t dims[5], const uint64_t strides_bytes[4],
+                const uint32_t box[5], CUtensorMapSwizzle swizzle);
 
 }  // namespace tc
 }  // namespace b200

@@ -219,6 +219,40 @@ def _infer(node: Node, shp, consts):
     raise UnsupportedNode("node '%s': ONNX operator %s is not implemented by this library" % (node.name, op))
 
 
+_AXES_AS_INPUT = {"ReduceMean": 18, "Squeeze": 13, "Unsqueeze": 13}  # opset from which `axes` is an input tensor
+
+
+def _to_opset12_form(node: Node, opset: int, consts) -> Node:
+    """Rewrites a node of a newer opset into the opset-12 form the rest of this package reads, or refuses it.
+
+    * Softmax / LogSoftmax without an `axis` attribute: the default is 1 up to opset 12 and -1 from opset 13 on.
+      (Either way `axis` is ONE numpy axis, as in the reference's pure expansions, pure_implementations.py:352-364,
+      :600-614.)
+    * ReduceMean (opset 18), Squeeze / Unsqueeze (opset 13): `axes` arrives as a second input. A constant one
+      becomes the attribute; a runtime one cannot be planned statically and is refused."""
+    op = node.op_type
+    if op in ("Softmax", "LogSoftmax") and "axis" not in node.attrs:
+        return Node(op, node.name, list(node.inputs), list(node.outputs), dict(node.attrs, axis=-1 if opset >= 13 else 1),
+                    node.domain)
+    if op in _AXES_AS_INPUT and len(node.inputs) > 1 and node.inputs[1]:
+        name = node.inputs[1]
+        if name not in consts:
+            raise UnsupportedNode("%s '%s': `axes` is a runtime tensor (opset >= %d form); only constant axes can "
+                                  "be planned" % (op, node.name, _AXES_AS_INPUT[op]))
+        axes = [int(a) for a in np.asarray(consts[name]).reshape(-1)]
+        attrs = dict(node.attrs)
+        if not axes:
+            if op == "ReduceMean" and attrs.get("noop_with_empty_axes", 0):
+                raise UnsupportedNode("ReduceMean '%s': noop_with_empty_axes is not supported" % node.name)
+            axes = None  # empty axes: reduce / squeeze over everything, the attribute-less meaning
+        if axes is not None:
+            attrs["axes"] = axes
+        return Node(op, node.name, [node.inputs[0]], list(node.outputs), attrs, node.domain)
+    if op == "Unsqueeze" and node.attrs.get("axes") is None:
+        raise UnsupportedNode("Unsqueeze '%s' has no axes" % node.name)
+    return node
+
+
 def specialize(model: Model, input_shapes: Sequence[Sequence[int]]) -> GraphIR:
     """Static-shape, constant-folded form of `model` for the given input shapes (graph input order)."""
     g: Graph = model.graph
@@ -244,6 +278,7 @@ def specialize(model: Model, input_shapes: Sequence[Sequence[int]]) -> GraphIR:
     for node in g.nodes:
         if node.domain not in ("", "ai.onnx"):
             raise UnsupportedNode("node '%s': operator domain '%s'" % (node.name, node.domain))
+        node = _to_opset12_form(node, model.opset, ir.consts)
         if node.op_type == "Constant":
             v = node.attr("value")
             if v is None:

@@ -44,6 +44,9 @@ class _Plan:
         self.fusion_stats = fusion.run_all(self.ir) if fuse else {}
         self._consts: Dict[str, torch.Tensor] = {}
         self._scratch: Dict[str, torch.Tensor] = {}
+        self._nhwc: Dict[str, tuple] = {}   # values kept in [N, H, W, C] between two convolutions -> that shape
+        if fuse:
+            self.fusion_stats["conv_nhwc_links"] = self._mark_conv_layouts()
         self.steps = []
         self._build()
 
@@ -65,6 +68,51 @@ class _Plan:
             t = torch.empty(numel, device=self.device, dtype=torch.float32)
             self._scratch[key] = t
         return t
+
+    # -- convolution layouts ---------------------------------------------------------------------------
+    def _conv_geometry(self, node):
+        ir = self.ir
+        x, w = ir.shapes[node.inputs[0]], tuple(ir.consts[node.inputs[1]].shape)
+        pads = tuple(node.attr("pads", [0, 0, 0, 0]))
+        strides = tuple(node.attr("strides", [1, 1]))
+        return x, w, pads, strides
+
+    def _conv_takes_nhwc(self, node) -> bool:
+        ir = self.ir
+        if node.inputs[1] not in ir.consts or (len(node.inputs) > 2 and node.inputs[2] and node.inputs[2] not in ir.consts):
+            return False
+        x, w, pads, strides = self._conv_geometry(node)
+        if len(x) != 4 or len(w) != 4 or node.attr("group", 1) != 1 or tuple(node.attr("dilations", [1, 1])) != (1, 1) or \
+                pads[0] != pads[2] or pads[1] != pads[3]:
+            return False
+        d = ops.ConvDesc(x[0], x[1], x[2], x[3], w[0], w[2], w[3], pads[0], pads[1], strides[0], strides[1], 0,
+                         ops._math(self.math_mode))
+        import ctypes
+        return bool(_lib.load().b200_conv2d_nhwc_supported(ctypes.byref(d)))
+
+    def _mark_conv_layouts(self) -> int:
+        """A value produced by one convolution and read only by the next stays in [N, H, W, C], the layout the
+        tensor-core kernel reads and writes natively: only the first input and the last output of a chain of
+        convolutions pay the NCHW <-> NHWC change. Returns the number of such links."""
+        ir = self.ir
+        consumers = ir.consumers()
+        links = 0
+        for node in ir.nodes:
+            if node.op_type != "Conv":
+                continue
+            out = node.outputs[0]
+            users = consumers.get(out, [])
+            if out in ir.outputs or len(users) != 1 or users[0].op_type != "Conv" or users[0].inputs[0] != out or \
+                    out in users[0].inputs[1:]:
+                continue
+            if not (self._conv_takes_nhwc(node) and self._conv_takes_nhwc(users[0])):
+                continue
+            n, m, oh, ow = ir.shapes[out]
+            self._nhwc[out] = (n, oh, ow, m)
+            node.attrs["y_nhwc"] = 1
+            users[0].attrs["x_nhwc"] = 1
+            links += 1
+        return links
 
     # -- planning ------------------------------------------------------------------------------------
     def _build(self):
@@ -97,7 +145,7 @@ class _Plan:
             out = node.outputs[0]
             r = rt(out)
             if r == out and r not in external:
-                shape = ir.shapes[out]
+                shape = self._nhwc.get(out, ir.shapes[out])
                 numel = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
                 if r in per_call:
                     self.per_call[r] = shape
@@ -203,6 +251,21 @@ class _Plan:
         group = node.attr("group", 1)
         relu = bool(node.attr("relu", 0))
         has_b = len(ins) > 2 and bool(ins[2])
+        x_nhwc, y_nhwc = bool(node.attr("x_nhwc", 0)), bool(node.attr("y_nhwc", 0))
+        const_filter = ins[1] in ir.consts and (not has_b or ins[2] in ir.consts)
+        if const_filter and (self.fusion_stats or x_nhwc or y_nhwc):
+            # constant filter: repacked (and split) once, when the plan is built -- what the reference's cuDNN
+            # expansion does with its descriptors in the SDFG init hook (cudnn_implementations.py:281-301)
+            conv = ops.PreparedConv(self.const(ins[1]), self.const(ins[2]) if has_b else None, pads=pads,
+                                    strides=strides, dilations=dil, group=group, relu=relu, math_mode=mm)
+            n = ir.shapes[ins[0]][0]
+            need = 0 if x_nhwc else int(np.prod(ir.shapes[ins[0]], dtype=np.int64)) + 64
+            ws = self.scratch("conv_ws", need).view(torch.uint8) if need else None
+
+            def run_prepared(env):
+                conv(env[ins[0]], out=env[out], x_nhwc=x_nhwc, y_nhwc=y_nhwc, workspace=ws)
+
+            return run_prepared
         need = ops.conv2d_workspace_bytes(ir.shapes[ins[0]], tuple(ir.consts[ins[1]].shape) if ins[1] in ir.consts
                                           else ir.shapes[ins[1]], pads, strides, mm)
         ws = self.scratch("conv_ws", (need + 3) // 4) if need else None
@@ -332,11 +395,8 @@ class ONNXModelB200:
         self.fuse = fuse
         self.math_mode = math_mode
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        if self.model.opset not in (0, 12):
-            import logging
-            logging.getLogger(__name__).warning(
-                "expected an opset-12 model, got opset %d; nodes whose definition changed may be refused",
-                self.model.opset)
+        # Models of other opsets are accepted: onnx_graph.specialize rewrites the nodes whose definition changed
+        # after opset 12 (Softmax / LogSoftmax default axis, `axes` as an input) or refuses them at plan time.
         _lib.load()  # fail now, not at the first call, when the CUDA library is missing
         self._plans: Dict[tuple, _Plan] = {}
         self.cuda_graph = bool(cuda_graph)

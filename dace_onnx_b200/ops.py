@@ -162,7 +162,9 @@ def gemm(A, B, C=None, out=None, *, alpha=1.0, beta=1.0, transA=0, transB=1, rel
             raise ValueError("Gemm: relu fusion needs a bias operand")
         return matmul(A, B, out, trans_b=True, math_mode=math_mode)
     C = _contig(C, "C")
-    if C.numel() == B.shape[0]:
+    # a per-column bias: [N], or [1, ..., 1, N]. Anything else (e.g. a per-row [M, 1] with M == N) broadcasts
+    # differently and takes the generic Add.
+    if C.numel() == B.shape[0] and C.dim() >= 1 and C.shape[-1] == B.shape[0]:
         return matmul(A, B, out, trans_b=True, epilogue=EPI_BIAS_RELU if relu else EPI_BIAS, bias=C.reshape(-1),
                       math_mode=math_mode)
     Y = matmul(A, B, out, trans_b=True, math_mode=math_mode)

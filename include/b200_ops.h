@@ -72,6 +72,14 @@ B200_API const char *b200_last_error_string(void);
  * expires (0 = clean). Synchronises the device: for tests and post-run checks, not hot paths. */
 B200_API int b200_device_status(void);
 
+/* Diagnostic: launches one tiny kernel (one warp) that waits on a barrier nothing will ever signal, with the
+ * bounded wait all tensor-core kernels of this library use, limited to `budget_cycles` (1 .. 1e8) GPU clock cycles.
+ * The wait expires, the kernel returns normally, and the next b200_device_status() reports B200_EDEVICE once
+ * (role mask 0x8000) and is clean afterwards. Lets a deployment check the failure-reporting path without making
+ * any real kernel fail. No counterpart in the reference (its library calls print and continue,
+ * daceml/onnx/environments/cudnn.py / include/daceml_cudnn.h:15-22). */
+B200_API int b200_selftest_wait_expiry(void *stream, int64_t budget_cycles);
+
 /* ------------------------------------------------------------------------------------------
  * Contractions.
  * b200_gemm_f32 replaces ONNXMatMul (daceml/onnx/op_implementations/pure_implementations.py:130-235,

@@ -144,5 +144,5 @@ def test_tf32_error_of_the_24_layer_forward(cuda, record_property):
           % (mx, rms, mx3, rms3))
     for k, v in (("tf32_max", mx), ("tf32_rms", rms), ("fp32x3_max", mx3), ("fp32x3_rms", rms3)):
         record_property(k, v)
-    assert mx < 5e-2 and rms < 5e-3          # inside the stated TF32 tolerance (rtol 2e-2 / atol 1e-2) on average
-    assert mx3 < 1e-3 and rms3 < 5e-5        # the fp32-accurate mode through 24 layers
+    assert mx < 5e-2 and rms < 1e-2          # measured: max 2.3e-2, rms 4.6e-3 (stated TF32 tolerance: rtol 2e-2 / atol 1e-2)
+    assert mx3 < 2e-4 and rms3 < 3e-5        # measured: max 2.9e-5, rms 5.6e-6

@@ -51,6 +51,19 @@ def test_fused_and_unfused_plans(cuda):
     assert plain.buffer_bytes < 4 * sum(int(np.prod(s)) for s in plain.ir.shapes.values()) / 2
 
 
+def test_conv_chain_stays_nhwc_between_convolutions(cuda):
+    g = golden("onnx_conv_stack")
+    fused = ONNXModelB200("conv_stack", _path("conv_stack"), fuse=True)
+    x = torch.from_numpy(g["x"])
+    plan = fused.plan(tuple(x.shape))
+    assert plan.fusion_stats["conv_relu"] == 2 and plan.fusion_stats["conv_nhwc_links"] == 1
+    convs = [n for n in plan.ir.nodes if n.op_type == "Conv"]
+    assert convs[0].attr("y_nhwc") == 1 and convs[1].attr("x_nhwc") == 1 and not convs[1].attr("y_nhwc", 0)
+    close(fused(x), graph_oracle.run(_path("conv_stack"), [g["x"]])[0], RTOL, ATOL)
+    plain = ONNXModelB200("conv_stack", _path("conv_stack"), fuse=False).plan(tuple(x.shape))
+    assert not any(n.attr("x_nhwc", 0) or n.attr("y_nhwc", 0) for n in plain.ir.nodes)
+
+
 def test_calling_conventions(cuda):
     g = golden("onnx_mlp")
     model = ONNXModelB200("mlp", open(_path("mlp"), "rb").read())

@@ -12,6 +12,7 @@ from dace_onnx_b200.onnx_graph import GraphIR, UnsupportedNode, specialize
 from dace_onnx_b200.onnx_model import clean_name
 from dace_onnx_b200.onnx_wire import Node
 from oracle import graph_oracle
+from oracle import pure_oracle as po
 
 CASES = ["mlp", "conv_stack", "norm_acts", "bert_layer", "bert_layer_nofold"]
 
@@ -183,3 +184,55 @@ def test_graph_oracle_is_unfused():
     y1 = graph_oracle.run(_load("bert_layer"), [x])[0]
     y2 = graph_oracle.run(_load("bert_layer_nofold"), [x])[0]
     assert y1.shape == y2.shape == (2, 32, 128)
+
+
+def _tiny_model(nodes, opset, inits=None, in_shape=(2, 3, 4), out="y"):
+    from dace_onnx_b200.onnx_wire import Graph, Model, ValueInfo
+    return Model(Graph("g", nodes, dict(inits or {}), [ValueInfo("x", np.float32, in_shape)],
+                       [ValueInfo(out, np.float32, None)]), opset)
+
+
+def test_newer_opsets_are_rewritten_or_refused():
+    """Nodes whose definition changed after opset 12 either run with their own opset's meaning or are refused
+    when the plan is built; none is silently evaluated with opset-12 defaults."""
+    x = np.random.default_rng(3).standard_normal((2, 3, 4)).astype(np.float32)
+    # Softmax / LogSoftmax without an axis attribute: axis 1 up to opset 12, the last axis from opset 13 on
+    for op, fn in (("Softmax", po.Softmax), ("LogSoftmax", po.LogSoftmax)):
+        for opset, axis in ((12, 1), (11, 1), (13, -1), (17, -1)):
+            m = _tiny_model([Node(op, "s", ["x"], ["y"])], opset)
+            ir = specialize(m, [(2, 3, 4)])
+            assert ir.nodes[0].attr("axis") == axis
+            np.testing.assert_allclose(graph_oracle.run(m, [x])[0].numpy(), fn(x, axis).numpy(), rtol=1e-6)
+        m = _tiny_model([Node(op, "s", ["x"], ["y"], {"axis": 0})], 13)      # an explicit axis is kept
+        assert specialize(m, [(2, 3, 4)]).nodes[0].attr("axis") == 0
+    # ReduceMean with axes as an input (opset 18): constant axes become the attribute
+    m = _tiny_model([Node("ReduceMean", "r", ["x", "ax"], ["y"], {"keepdims": 1})], 18, {"ax": np.asarray([-1], np.int64)})
+    ir = specialize(m, [(2, 3, 4)])
+    assert ir.nodes[0].attr("axes") == [-1] and ir.nodes[0].inputs == ["x"] and ir.shapes["y"] == (2, 3, 1)
+    np.testing.assert_allclose(graph_oracle.run(m, [x])[0].numpy(), x.mean(-1, keepdims=True), rtol=1e-6)
+    # empty constant axes = reduce over everything; with noop_with_empty_axes it is refused
+    m = _tiny_model([Node("ReduceMean", "r", ["x", "ax"], ["y"], {"keepdims": 0})], 18, {"ax": np.zeros(0, np.int64)})
+    assert specialize(m, [(2, 3, 4)]).shapes["y"] == ()
+    m = _tiny_model([Node("ReduceMean", "r", ["x", "ax"], ["y"], {"noop_with_empty_axes": 1})], 18,
+                    {"ax": np.zeros(0, np.int64)})
+    with pytest.raises(UnsupportedNode):
+        specialize(m, [(2, 3, 4)])
+    # runtime axes cannot be planned
+    from dace_onnx_b200.onnx_wire import ValueInfo
+    m = _tiny_model([Node("ReduceMean", "r", ["x", "ax"], ["y"])], 18)
+    m.graph.inputs.append(ValueInfo("ax", np.int64, (1,)))
+    with pytest.raises(UnsupportedNode, match="runtime tensor"):
+        specialize(m, [(2, 3, 4), (1,)])
+    # Squeeze / Unsqueeze with axes as an input (opset 13)
+    m = _tiny_model([Node("Unsqueeze", "u", ["x", "ax"], ["t"]), Node("Squeeze", "q", ["t", "ax"], ["s"]),
+                     Node("Relu", "r", ["s"], ["y"])], 13, {"ax": np.asarray([1], np.int64)})
+    ir = specialize(m, [(2, 3, 4)])
+    assert ir.shapes["t"] == (2, 1, 3, 4) and ir.shapes["s"] == (2, 3, 4)
+    np.testing.assert_array_equal(graph_oracle.run(m, [x])[0].numpy(), np.maximum(x, 0))
+    m = _tiny_model([Node("Unsqueeze", "u", ["x", "ax"], ["y"])], 13)
+    m.graph.inputs.append(ValueInfo("ax", np.int64, (1,)))
+    with pytest.raises(UnsupportedNode):
+        specialize(m, [(2, 3, 4), (1,)])
+    m = _tiny_model([Node("Unsqueeze", "u", ["x"], ["y"])], 13)              # neither attribute nor input
+    with pytest.raises(UnsupportedNode):
+        specialize(m, [(2, 3, 4)])

@@ -64,6 +64,7 @@ def hooks():
 HOOK_HEAD = """
 extern "C" int cudaMalloc(void **, size_t);
 extern "C" int cudaFree(void *);
+static const int cudaSuccess = 0;
 """
 HOOK_WRAP = """
 void hook_{i}(State *__state) {{
