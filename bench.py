@@ -25,6 +25,7 @@ sys.path.insert(0, ROOT)
 WORKLOADS = {
     # name: (layers, hidden, heads, ffn, batch, seq, math mode)
     "bert_large_x24_b1024_s384_tf32": (24, 1024, 16, 4096, 1024, 384, "tf32"),
+    "bert_large_x24_b1024_s384_bf16": (24, 1024, 16, 4096, 1024, 384, "bf16"),
     "bert_base_x1_b64_s512_fp32x3": (1, 768, 12, 3072, 64, 512, "fp32x3"),
     "bert_base_x1_b64_s512_tf32": (1, 768, 12, 3072, 64, 512, "tf32"),
 }
@@ -241,7 +242,8 @@ def run_b200(args, wl):
         d[2] += nbytes
         d[3] += 1
     peaks = measured_peaks()
-    tf32_peak = peaks["bf16_sustained"] / 2.0  # no TF32 figure is measured; half the sustained bf16 rate
+    # no TF32 figure is measured: half the sustained bf16 rate (the bf16 workload is held against the bf16 rate itself)
+    tf32_peak = peaks["bf16_sustained"] / (1.0 if mode == "bf16" else 2.0)
     ops_report = {}
     for kind, (sec, flops, nbytes, n) in sorted(per_kind.items()):
         entry = {"launches": n, "ms_per_step": sec * 1e3 / args.steps, "share": None}
@@ -275,9 +277,10 @@ def run_b200(args, wl):
     cap = NCU_TRAFFIC["gemm_tc_pair_kernel"]
     traffic = cap["dram_bytes"] / cap["algorithmic_bytes"] * alg_bytes
     achieved = g[1] / g[0] / 1e12
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<256, K-major> (TF32 dense projections, CTA pairs)",
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_pair_kernel<256, K-major> (%s dense projections, CTA pairs)" % mode.upper(),
                 "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                "peak_source": "%s bf16 sustained / 2 (TF32 runs at half the bf16 rate)" % peaks["source"],
+                "peak_source": ("%s bf16 sustained" if mode == "bf16" else
+                                "%s bf16 sustained / 2 (TF32 runs at half the bf16 rate)") % peaks["source"],
                 "avg_launch_ms": g[0] * 1e3 / max(g[3], 1), "traffic": traffic,
                 "traffic_unit": "bytes per launch (scaled from the ncu capture in %s)" % cap["profile"],
                 "algorithmic_bytes": alg_bytes}
@@ -299,7 +302,7 @@ def run_b200(args, wl):
         line = {
             "metric": METRIC, "value": batch / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "tf32" if mode == "tf32" else "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": mode if mode in ("tf32", "bf16") else "f32", "data": "synthetic",
             "config": {"workload": wl, "layers": layers, "hidden": hidden, "heads": heads, "ffn": ffn,
                        "global_batch": batch, "seq_len": seq, "parallelism": "batch-sharded x%d, output all-gather" % world,
                        "math_mode": mode, "micro_batch": min(enc.micro_batch, local),
@@ -543,6 +546,8 @@ def kernel_cases(device):
         "softmax_c4": softmax_c4, "layernorm_c4": layernorm_c4,
         "gemm_tf32_qkv": gemm(16384, 3072, 1024, "tf32"), "gemm_tf32_ffn1": gemm(16384, 4096, 1024, "tf32", EPI_BIAS_GELU),
         "gemm_tf32_ffn2": gemm(16384, 1024, 4096, "tf32"), "gemm_tf32_proj": gemm(16384, 1024, 1024, "tf32"),
+        "gemm_bf16_qkv": gemm(16384, 3072, 1024, "bf16"), "gemm_bf16_ffn1": gemm(16384, 4096, 1024, "bf16", EPI_BIAS_GELU),
+        "gemm_bf16_ffn2": gemm(16384, 1024, 4096, "bf16"),
         "gemm_fp32x3_ffn1": gemm(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU), "gemm_fp32x3_proj": gemm(16384, 768, 768, "fp32x3"),
         "gemm_fp32x3_ffn1_no_workspace": gemm_no_workspace(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
@@ -617,7 +622,7 @@ def run_kernel_case(args):
         ms, flops, nbytes, bound, nsets = time_case(cases[name], args.steps, args.warmup)
         _lib.device_status()
         if bound == "tensor":
-            peak = peaks["bf16"] / 2.0  # a kernel timed alone: burst figure
+            peak = peaks["bf16"] / (1.0 if "bf16" in name else 2.0)  # a kernel timed alone: burst figure (TF32 = bf16 / 2)
             achieved, unit = flops / (ms * 1e-3) / 1e12, "TFLOP/s"
         else:
             peak, achieved, unit = peaks["hbm_gbs"], nbytes / (ms * 1e-3) / 1e9, "GB/s"

@@ -10,13 +10,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200ops.so")
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, EWORKSPACE, EDEVICE = 0, -1, -2, -3, -4, -5
-MATH_FP32X3, MATH_TF32, MATH_FP32 = 0, 1, 2
+MATH_FP32X3, MATH_TF32, MATH_FP32, MATH_BF16 = 0, 1, 2, 3
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_BIAS_RESIDUAL, EPI_SCALE = range(6)
 ADD, SUB, MUL, DIV, POW = range(5)
 SQRT, ERF, RELU, GELU = range(4)
 CONV_X_NHWC, CONV_Y_NHWC = 1, 2
 
-MATH_MODES = {"fp32x3": MATH_FP32X3, "tf32": MATH_TF32, "fp32": MATH_FP32}
+MATH_MODES = {"fp32x3": MATH_FP32X3, "tf32": MATH_TF32, "fp32": MATH_FP32, "bf16": MATH_BF16}
 
 
 class B200Error(RuntimeError):

@@ -22,8 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 INCLUDE_DIR = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libb200ops.so")
 
-MATH_MODE_ENV = "B200_MATH_MODE"  # fp32x3 (default) | tf32 | fp32, read when a node is expanded
-_MATH = {"fp32x3": 0, "tf32": 1, "fp32": 2}
+MATH_MODE_ENV = "B200_MATH_MODE"  # fp32x3 (default) | tf32 | bf16 | fp32, read when a node is expanded
+_MATH = {"fp32x3": 0, "tf32": 1, "fp32": 2, "bf16": 3}
 _BINARY = {"Add": 0, "Sub": 1, "Mul": 2, "Div": 3, "Pow": 4}
 _UNARY = {"Sqrt": 0, "Erf": 1, "Relu": 2}
 
@@ -342,8 +342,8 @@ def _register():
         _REGISTERED[op] = op_implementation(op=op, name="b200")(Impl)
 
     def gemm_build(node, d, ws, trans_b, bias):
-        # fp32-accurate mode: the node gets device scratch from the SDFG state, like the cuDNN expansion
-        if math_mode() != 0:
+        # fp32-accurate and bf16 modes: the node gets device scratch from the SDFG state, like the cuDNN expansion
+        if math_mode() not in (0, 3):
             return tasklet_matmul(d["A"].shape, d["B"].shape, node.label, trans_b=trans_b, bias=bias), None
         fields, init, fini = gemm_env_code(d["A"].shape, d["B"].shape, ws, trans_b=trans_b, bias=bias)
 

@@ -122,14 +122,18 @@ int gemm_entry(void *stream, const b200_gemm_desc *desc, const float *A, const f
   }
   if (d.epilogue != B200_EPI_BIAS_RESIDUAL) residual = nullptr;
   if (d.epilogue == B200_EPI_NONE || d.epilogue == B200_EPI_SCALE) bias = nullptr;
-  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
+  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32 &&
+      d.math_mode != B200_MATH_BF16)
     return fail(B200_EINVAL, "gemm: unknown math mode %d", d.math_mode);
 
   flatten_dense_batch(d);
 
   // Tensor-core path whenever TMA can address the operands; the CUDA-core kernel otherwise
   // (and when the caller asks for plain fp32 arithmetic).
-  if (d.math_mode != B200_MATH_FP32 && gemm_tc_supported(d, A, B, Y))
+  // (BF16 copies its operands into the workspace, so the TMA addressing rules do not bind its inputs.)
+  const bool bf16_dense = d.math_mode == B200_MATH_BF16 && d.batch_outer * d.batch_inner == 1 && d.M <= 0x7fffffffLL &&
+                          d.N <= 0x7fffffffLL && d.K >= 1 && d.K <= 0x7fffffffLL;
+  if (d.math_mode != B200_MATH_FP32 && (bf16_dense || gemm_tc_supported(d, A, B, Y)))
     return gemm_tc(st, d, A, B, bias, residual, Y, workspace, workspace_bytes);
   return gemm_simt(st, d, A, B, bias, residual, Y);
 }
@@ -155,7 +159,10 @@ extern "C" B200_API int b200_gemm_ws_f32(void *stream, const b200_gemm_desc *des
 
 extern "C" B200_API int b200_attention_supported(const b200_attention_desc *desc, const float *Q, const float *K,
                                                  const float *V, const float *out) {
-  return desc && Q && K && V && out && desc->scale > 0.f && attention_tc_supported(*desc, Q, K, V, out) ? 1 : 0;
+  if (!desc || !Q || !K || !V || !out || !(desc->scale > 0.f)) return 0;
+  b200_attention_desc d = *desc;
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;  // the fused kernel computes a BF16 request in TF32
+  return attention_tc_supported(d, Q, K, V, out) ? 1 : 0;
 }
 
 extern "C" B200_API int b200_attention_f32(void *stream, const b200_attention_desc *desc, const float *Q,
@@ -167,10 +174,12 @@ extern "C" B200_API int b200_attention_f32(void *stream, const b200_attention_de
   if (!Q || !K || !V || !out) return fail(B200_EINVAL, "attention: null pointer");
   if (!b200_attention_supported(desc, Q, K, V, out))
     return fail(B200_EUNSUPPORTED,
-                "attention: fused kernel needs TF32 mode, head_dim 64, seq %% 32 == 0, aligned strides "
+                "attention: fused kernel needs the TF32 (or BF16) mode, head_dim 64, seq %% 32 == 0, aligned strides "
                 "(got mode %d, head_dim %lld, seq %lld); run the unfused nodes instead",
                 desc->math_mode, (long long)desc->head_dim, (long long)desc->seq);
-  return attention_tc((cudaStream_t)stream, *desc, Q, K, V, out);
+  b200_attention_desc d = *desc;
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;
+  return attention_tc((cudaStream_t)stream, d, Q, K, V, out);
 }
 
 static bool conv_out_shape(const b200_conv_desc &d, int64_t *oh, int64_t *ow) {
@@ -186,7 +195,7 @@ namespace {
 inline size_t up256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 // Argument checks shared by the convolution entry points; on success *bias is null unless the epilogue uses it.
-int conv_check(const char *who, const b200_conv_desc &d, const float *X, const void *W, const float **bias,
+int conv_check(const char *who, b200_conv_desc &d, const float *X, const void *W, const float **bias,
                const float *Y, int64_t *OH, int64_t *OW, bool *empty) {
   if (d.N < 0 || d.C < 1 || d.H < 1 || d.W < 1 || d.M < 0) return fail(B200_EINVAL, "%s: bad extent", who);
   if (!conv_out_shape(d, OH, OW)) return fail(B200_EINVAL, "%s: bad kernel/pad/stride", who);
@@ -197,18 +206,28 @@ int conv_check(const char *who, const b200_conv_desc &d, const float *X, const v
     return fail(B200_EINVAL, "%s: unsupported epilogue %d", who, d.epilogue);
   if (d.epilogue != B200_EPI_NONE && !*bias) return fail(B200_EINVAL, "%s: epilogue %d needs a bias", who, d.epilogue);
   if (d.epilogue == B200_EPI_NONE) *bias = nullptr;
-  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
+  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32 &&
+      d.math_mode != B200_MATH_BF16)
     return fail(B200_EINVAL, "%s: unknown math mode %d", who, d.math_mode);
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;  // no bf16 convolution kernel: TF32 is more accurate
   return B200_OK;
 }
 }  // namespace
 
 // b200_conv2d_f32 = prepare + run on the caller's workspace: [NHWC copy of X | prepared filter]
+// the descriptor as the kernels see it: a BF16 request runs in TF32
+static b200_conv_desc conv_effective(const b200_conv_desc *desc) {
+  b200_conv_desc d = *desc;
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;
+  return d;
+}
+
 extern "C" B200_API size_t b200_conv2d_workspace_bytes(const b200_conv_desc *desc) {
   if (!desc) return 0;
+  const b200_conv_desc d = conv_effective(desc);
   // alignment of X is unknown here; the tensor-core path needs this much whenever the shape allows it
-  if (!conv2d_tc_supported(*desc, nullptr)) return 0;
-  return up256(conv2d_run_workspace_bytes(*desc, 0)) + conv2d_filter_bytes(*desc);
+  if (!conv2d_tc_supported(d, nullptr)) return 0;
+  return up256(conv2d_run_workspace_bytes(d, 0)) + conv2d_filter_bytes(d);
 }
 
 extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc, const float *X, const float *W,
@@ -234,7 +253,7 @@ extern "C" B200_API int b200_conv2d_f32(void *stream, const b200_conv_desc *desc
 
 extern "C" B200_API size_t b200_conv2d_filter_bytes(const b200_conv_desc *desc) {
   if (!desc || desc->M < 1 || desc->C < 1 || desc->KH < 1 || desc->KW < 1) return 0;
-  return conv2d_filter_bytes(*desc);
+  return conv2d_filter_bytes(conv_effective(desc));
 }
 
 extern "C" B200_API int b200_conv2d_prepare_filter_f32(void *stream, const b200_conv_desc *desc, const float *W,
@@ -243,18 +262,24 @@ extern "C" B200_API int b200_conv2d_prepare_filter_f32(void *stream, const b200_
   if (desc->C < 1 || desc->M < 0 || desc->KH < 1 || desc->KW < 1) return fail(B200_EINVAL, "conv(prepare): bad extent");
   if (desc->M == 0) return B200_OK;
   if (!W) return fail(B200_EINVAL, "conv(prepare): null pointer");
-  if (desc->math_mode != B200_MATH_FP32X3 && desc->math_mode != B200_MATH_TF32 && desc->math_mode != B200_MATH_FP32)
+  if (desc->math_mode != B200_MATH_FP32X3 && desc->math_mode != B200_MATH_TF32 && desc->math_mode != B200_MATH_FP32 &&
+      desc->math_mode != B200_MATH_BF16)
     return fail(B200_EINVAL, "conv(prepare): unknown math mode %d", desc->math_mode);
-  return conv2d_prepare_filter((cudaStream_t)stream, *desc, W, filter, filter_bytes);
+  b200_conv_desc d = *desc;
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;
+  return conv2d_prepare_filter((cudaStream_t)stream, d, W, filter, filter_bytes);
 }
 
 extern "C" B200_API int b200_conv2d_nhwc_supported(const b200_conv_desc *desc) {
-  return desc && desc->C >= 1 && desc->M >= 1 && desc->KH >= 1 && desc->KW >= 1 && conv2d_nhwc_supported(*desc) ? 1 : 0;
+  return desc && desc->C >= 1 && desc->M >= 1 && desc->KH >= 1 && desc->KW >= 1 &&
+                 conv2d_nhwc_supported(conv_effective(desc))
+             ? 1
+             : 0;
 }
 
 extern "C" B200_API size_t b200_conv2d_prepared_workspace_bytes(const b200_conv_desc *desc, int flags) {
   if (!desc || desc->N < 1 || desc->C < 1 || desc->H < 1 || desc->W < 1) return 0;
-  return conv2d_run_workspace_bytes(*desc, flags);
+  return conv2d_run_workspace_bytes(conv_effective(desc), flags);
 }
 
 extern "C" B200_API int b200_conv2d_prepared_f32(void *stream, const b200_conv_desc *desc, int flags, const float *X,

@@ -74,8 +74,10 @@ extern "C" B200_API int b200_conv2d_static_f32(void *stream, const b200_conv_des
     return fail(B200_EINVAL, "conv(static): unsupported epilogue %d", d.epilogue);
   if (d.epilogue != B200_EPI_NONE && !bias) return fail(B200_EINVAL, "conv(static): epilogue %d needs a bias", d.epilogue);
   if (d.epilogue == B200_EPI_NONE) bias = nullptr;
-  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32)
+  if (d.math_mode != B200_MATH_FP32X3 && d.math_mode != B200_MATH_TF32 && d.math_mode != B200_MATH_FP32 &&
+      d.math_mode != B200_MATH_BF16)
     return fail(B200_EINVAL, "conv(static): unknown math mode %d", d.math_mode);
+  if (d.math_mode == B200_MATH_BF16) d.math_mode = B200_MATH_TF32;  // as in b200_conv2d_f32
 
   // Shapes the tensor cores cannot take run on the CUDA-core kernel, which uses no scratch at all.
   if (!conv2d_tc_supported(d, X)) return conv2d_simt(st, d, X, W, bias, Y, OH, OW);

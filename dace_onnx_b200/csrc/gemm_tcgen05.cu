@@ -19,6 +19,7 @@
 // Every mbarrier wait is bounded by a cycle budget; on expiry the CTA sets a bit in the device
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "contract.cuh"
@@ -201,12 +202,15 @@ struct Cfg {
   static constexpr int kColsPerWarp = BN / kWarpsPerQuarter;
 };
 
-template <int BN, bool B_MN, bool SPLIT3, bool CONV>
+// BF16: A and B are bf16 (64 values of K per 128-byte row, kind::f16 MMAs with K = 16); only with K-major B,
+// without SPLIT3 / CONV. Tiles, stages and descriptors have the same byte geometry as the TF32 form.
+template <int BN, bool B_MN, bool SPLIT3, bool CONV, bool BF16 = false>
 __global__ void __launch_bounds__(Cfg<BN, SPLIT3>::kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
   using C = Cfg<BN, SPLIT3>;
   constexpr int kStages = C::kStages;
+  constexpr int BKE = BF16 ? 64 : BK;  // elements of K per k-block (one 128-byte row)
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors address.
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -292,7 +296,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (++cv_kw == p.cv.KW) { cv_kw = 0; ++cv_kh; }
             }
           } else {
-            tma_load_4d(stage_a(s), &map_a, bar_full + 8 * s, kb * BK, m_t * BM, bi * p.a_bi, bo * p.a_bo);
+            tma_load_4d(stage_a(s), &map_a, bar_full + 8 * s, kb * BKE, m_t * BM, bi * p.a_bi, bo * p.a_bo);
           }
           if (B_MN) {
 #pragma unroll
@@ -300,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tma_load_4d(stage_b(s) + j * (BK * 128), &map_b, bar_full + 8 * s, n_t * BN + 32 * j, kb * BK,
                           bi * p.b_bi, bo * p.b_bo);
           } else {
-            tma_load_4d(stage_b(s), &map_b, bar_full + 8 * s, kb * BK, n_t * BN, bi * p.b_bi, bo * p.b_bo);
+            tma_load_4d(stage_b(s), &map_b, bar_full + 8 * s, kb * BKE, n_t * BN, bi * p.b_bi, bo * p.b_bo);
           }
           if (++s == kStages) { s = 0; ph ^= 1; }
         }
@@ -320,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // per-MMA instruction count minimal matters: a single thread issues the MMAs, and with
       // descriptor construction inside the loop its instruction latency (~140 clk per MMA), not the
       // tensor core (128 clk per N=256 MMA), bounded the loop.
-      constexpr uint32_t idesc = make_idesc(BN, B_MN);
+      constexpr uint32_t idesc = BF16 ? make_idesc_bf16(128, BN) : make_idesc(BN, B_MN);
       constexpr uint32_t kStage16 = C::kStageBytes >> 4;
       constexpr uint32_t kAStep = (UMMA_K * 4) >> 4;                         // 32 B inside the swizzle row
       constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);  // next 8 k-rows, or 32 B
@@ -355,6 +359,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 umma_tf32_ts(d_tmem, a_hi_t + 32, b_hi + kk * kBStep, idesc, accumulate);      // lo * hi
                 umma_tf32_ts(d_tmem, a_hi_t, b_hi + kBLo16 + kk * kBStep, idesc, 1u);          // hi * lo
                 umma_tf32_ts(d_tmem, a_hi_t, b_hi + kk * kBStep, idesc, 1u);                   // hi * hi
+              } else if (BF16) {
+                umma_bf16(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);
               } else {
                 umma_tf32(d_tmem, a_hi + kk * kAStep, b_hi + kk * kBStep, idesc, accumulate);
               }
@@ -551,12 +557,13 @@ struct Cfg2 {
   static constexpr int kColsPerWarp = BN / kWarpsPerQuarter;
 };
 
-template <int BN, bool B_MN>
+template <int BN, bool B_MN, bool BF16 = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2<BN>::kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
   using C = Cfg2<BN>;
   constexpr int kStages = C::kStages;
+  constexpr int BKE = BF16 ? 64 : BK;  // elements of K per k-block (one 128-byte row)
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * C::kStageBytes);
@@ -626,7 +633,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int h = 0; h < C::kKbPerStage; ++h) {
             const uint32_t a_dst = stage + h * A_STAGE_BYTES;
             const uint32_t b_dst = stage + C::kKbPerStage * A_STAGE_BYTES + h * C::kBHalfBytes;
-            const int k0 = (kb + h) * BK;
+            const int k0 = (kb + h) * BKE;
             if (rank == 0) {
               tma_load_4d(a_dst, &map_a, full, k0, row0, bi * p.a_bi, bo * p.a_bo);
               if (B_MN) {
@@ -654,7 +661,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (even CTA only) -------------------------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = make_idesc_pair(BN, B_MN);
+      constexpr uint32_t idesc = BF16 ? make_idesc_bf16(256, BN) : make_idesc_pair(BN, B_MN);
       constexpr uint32_t kStage16 = C::kStageBytes >> 4;
       constexpr uint32_t kAStep = (UMMA_K * 4) >> 4;
       constexpr uint32_t kBStep = B_MN ? (1024 >> 4) : ((UMMA_K * 4) >> 4);
@@ -679,9 +686,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int h = 0; h < C::kKbPerStage; ++h) {
 #pragma unroll
-            for (int kk = 0; kk < BK / UMMA_K; ++kk)
-              umma_tf32_pair(d_tmem, a_d + h * (A_STAGE_BYTES >> 4) + kk * kAStep,
-                             b_d + h * (C::kBHalfBytes >> 4) + kk * kBStep, idesc, (h > 0 || kk > 0) ? 1u : first);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              if (BF16)
+                umma_bf16_pair(d_tmem, a_d + h * (A_STAGE_BYTES >> 4) + kk * kAStep,
+                               b_d + h * (C::kBHalfBytes >> 4) + kk * kBStep, idesc, (h > 0 || kk > 0) ? 1u : first);
+              else
+                umma_tf32_pair(d_tmem, a_d + h * (A_STAGE_BYTES >> 4) + kk * kAStep,
+                               b_d + h * (C::kBHalfBytes >> 4) + kk * kBStep, idesc, (h > 0 || kk > 0) ? 1u : first);
+            }
           }
           // the stage is reusable in both CTAs once these MMAs have read it
           umma_commit_pair_both(bar_empty + 8 * s, 3);
@@ -1054,10 +1066,10 @@ void batch_axis(int64_t extent, int64_t stride_elems, uint64_t fallback_bytes, u
   }
 }
 
-template <int BN, bool B_MN, bool SPLIT3, bool CONV = false>
+template <int BN, bool B_MN, bool SPLIT3, bool CONV = false, bool BF16 = false>
 int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   using C = Cfg<BN, SPLIT3>;
-  auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3, CONV>;
+  auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3, CONV, BF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
     return fail(B200_ECUDA, "gemm(tc): cannot set dynamic shared memory to %d", C::kSmemBytes);
   const int64_t grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
@@ -1065,10 +1077,10 @@ int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, Ge
   return check_launch("gemm_tc");
 }
 
-template <int BN, bool B_MN>
+template <int BN, bool B_MN, bool BF16 = false>
 int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   using C = Cfg2<BN>;
-  auto kern = gemm_tc_pair_kernel<BN, B_MN>;
+  auto kern = gemm_tc_pair_kernel<BN, B_MN, BF16>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
     return fail(B200_ECUDA, "gemm(tc pair): cannot set dynamic shared memory to %d", C::kSmemBytes);
   // A persistent grid must not exceed the clusters the device can hold at once (both CTAs of a
@@ -1155,6 +1167,43 @@ int launch_conv_bn(cudaStream_t st, int bn, const CUtensorMap &ma, const CUtenso
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// fp32 [rows, cols] (row pitch ld) -> bf16 [rows, colsp], round-to-nearest-even, columns past `cols` zero; eight
+// outputs (one 16-byte store) per thread. colsp is a multiple of 8.
+__global__ void __launch_bounds__(256)
+convert_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int64_t rows, int64_t cols, int64_t ld,
+                    int64_t colsp) {
+  const int64_t per_row = colsp >> 3, total = rows * per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / per_row, c = (i - r * per_row) << 3;
+    const float *src = x + r * ld + c;
+    float v[8];
+    if (c + 8 <= cols && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+      const float4 a = ld_stream4(src), b = ld_stream4(src + 4);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = c + j < cols ? src[j] : 0.f;
+    }
+    __nv_bfloat162 q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    *reinterpret_cast<uint4 *>(out + r * colsp + c) = *reinterpret_cast<const uint4 *>(q);
+  }
+}
+
+// fp32 [rows, cols] (row pitch ld) -> bf16 [cols, rowsp]: the transpose, so that a [K, N] operand becomes K-major
+__global__ void __launch_bounds__(256)
+convert_bf16_transpose_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ out, int64_t rows, int64_t cols,
+                              int64_t ld, int64_t rowsp) {
+  __shared__ float tile[32][33];
+  const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int k = ty; k < 32; k += 8) tile[k][tx] = (r0 + k < rows && c0 + tx < cols) ? x[(r0 + k) * ld + c0 + tx] : 0.f;
+  __syncthreads();
+  for (int k = ty; k < 32; k += 8)
+    if (c0 + k < cols && r0 + tx < rowsp) out[(c0 + k) * rowsp + r0 + tx] = __float2bfloat16_rn(tile[tx][k]);
+}
+
 int pick_bn(int64_t N, bool split3) {
   const int cands[3] = {256, 128, 64};
   int best = 64;
@@ -1209,6 +1258,23 @@ int tc::encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], 
 }
 
 
+int tc::encode_map_bf16(CUtensorMap *map, const void *base, uint64_t k, uint64_t rows, uint64_t pitch_bytes,
+                        uint32_t box_k, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t gdim[4] = {k, rows, 1, 1};
+  cuuint64_t gstr[3] = {pitch_bytes, pitch_bytes * rows, pitch_bytes * rows};
+  cuuint32_t box[4] = {box_k, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(B200_ECUDA, "cuTensorMapEncodeTiled (bf16) failed (%d): k %llu rows %llu pitch %llu box {%u,%u}", (int)r,
+                (unsigned long long)k, (unsigned long long)rows, (unsigned long long)pitch_bytes, box_k, box_rows);
+  return B200_OK;
+}
+
 int tc::encode_map5(CUtensorMap *map, const float *base, const uint64_t dims[5], const uint64_t strides_bytes[4],
                     const uint32_t box[5], CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
@@ -1251,14 +1317,93 @@ static bool pair3_qualifies(const b200_gemm_desc &d) {
   return d.math_mode == B200_MATH_FP32X3 && d.batch_outer * d.batch_inner == 1 && d.M > BM && cols % 4 == 0;
 }
 
+// BF16 mode: one matrix (no batch). Both operands are converted into the workspace, K padded to a multiple of 8.
+static bool bf16_qualifies(const b200_gemm_desc &d) {
+  return d.math_mode == B200_MATH_BF16 && d.batch_outer * d.batch_inner == 1;
+}
+static size_t bf16_operand_bytes(int64_t rows, int64_t K) { return align256((size_t)rows * (size_t)((K + 7) / 8 * 8) * 2); }
+
 size_t gemm_tc_workspace_bytes(const b200_gemm_desc &d) {
+  if (bf16_qualifies(d)) return bf16_operand_bytes(d.M, d.K) + bf16_operand_bytes(d.N, d.K);
   if (!pair3_qualifies(d)) return 0;
   const int64_t rows = d.trans_b ? d.N : d.K, cols = d.trans_b ? d.K : d.N;
   return 2 * align256((size_t)rows * (size_t)cols * 4);
 }
 
-int gemm_tc(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
+// BF16 mode: A and B are rounded to bf16 into the workspace (B transposed to [N, K] when it is given as [K, N]), then
+// the same tile kernels run with kind::f16 MMAs (K = 16 per instruction, twice the TF32 rate), fp32 accumulate.
+static int gemm_tc_bf16(cudaStream_t st, const b200_gemm_desc &d, const float *A, const float *B, const float *bias,
+                        const float *residual, float *Y, void *workspace, size_t workspace_bytes) {
+  const size_t a_bytes = bf16_operand_bytes(d.M, d.K), b_bytes = bf16_operand_bytes(d.N, d.K);
+  if (!workspace || workspace_bytes < a_bytes + b_bytes)
+    return fail(B200_EWORKSPACE, "gemm(bf16): the BF16 mode converts its operands into a workspace of %zu bytes "
+                                 "(b200_gemm_workspace_bytes); call b200_gemm_ws_f32", a_bytes + b_bytes);
+  if (!aligned16(workspace)) return fail(B200_EINVAL, "gemm(bf16): workspace must be 16-byte aligned");
+  const int64_t Kp = (d.K + 7) / 8 * 8;
+  __nv_bfloat16 *a16 = static_cast<__nv_bfloat16 *>(workspace);
+  __nv_bfloat16 *b16 = reinterpret_cast<__nv_bfloat16 *>(static_cast<char *>(workspace) + a_bytes);
+  auto grid_for = [](int64_t work) {
+    int64_t g = (work + 255) / 256;
+    return (unsigned)(g > (int64_t)kNumSMs * 16 ? (int64_t)kNumSMs * 16 : (g < 1 ? 1 : g));
+  };
+  convert_bf16_kernel<<<grid_for(d.M * (Kp / 8)), 256, 0, st>>>(A, a16, d.M, d.K, d.lda, Kp);
+  if (int rc = check_launch("convert_bf16(A)")) return rc;
+  if (d.trans_b) {
+    convert_bf16_kernel<<<grid_for(d.N * (Kp / 8)), 256, 0, st>>>(B, b16, d.N, d.K, d.ldb, Kp);
+  } else {
+    if ((d.K + 31) / 32 > 65535) return fail(B200_EUNSUPPORTED, "gemm(bf16): K too large for the operand transpose");
+    dim3 grid((unsigned)((d.N + 31) / 32), (unsigned)((Kp + 31) / 32));
+    convert_bf16_transpose_kernel<<<grid, 256, 0, st>>>(B, b16, d.K, d.N, d.ldb, Kp);
+  }
+  if (int rc = check_launch("convert_bf16(B)")) return rc;
+
+  const int bn = pick_bn(d.N, false);
+  const bool pair = bn == 256 && d.M > BM;
+  CUtensorMap ma, mb;
+  if (int rc = encode_map_bf16(&ma, a16, (uint64_t)d.K, (uint64_t)d.M, (uint64_t)Kp * 2, 64, BM)) return rc;
+  if (int rc = encode_map_bf16(&mb, b16, (uint64_t)d.K, (uint64_t)d.N, (uint64_t)Kp * 2, 64, (uint32_t)(pair ? bn / 2 : bn)))
+    return rc;
+  GemmParams p{};
+  auto aligned_to = [&](int elems) {
+    const uintptr_t mask = (uintptr_t)elems * 4 - 1;
+    return (reinterpret_cast<uintptr_t>(Y) & mask) == 0 && (!residual || (reinterpret_cast<uintptr_t>(residual) & mask) == 0) &&
+           d.ldy % elems == 0;
+  };
+  p.vec = aligned_to(8) ? 8 : aligned_to(4) ? 4 : 1;
+  p.M = d.M;
+  p.N = d.N;
+  p.num_kb = (int)((d.K + 63) / 64);
+  p.num_m_tiles = (int)((d.M + BM - 1) / BM);
+  p.num_n_tiles = (int)((d.N + bn - 1) / bn);
+  p.batch_inner = 1;
+  p.num_tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
+  p.ldy = d.ldy;
+  p.epilogue = d.epilogue;
+  p.scale = d.scale;
+  p.bias = bias;
+  p.residual = residual;
+  p.Y = Y;
+  p.status = device_status_ptr();
+  if (!p.status) return fail(B200_ECUDA, "gemm(bf16): device status word unavailable");
+  if (pair) {
+    p.num_m_tiles = (int)((d.M + 2 * BM - 1) / (2 * BM));
+    p.num_tiles_batch = 1;
+    return launch_pair<256, false, true>(st, ma, mb, p);
+  }
+  switch (bn) {
+    case 64: return launch_cfg<64, false, false, false, true>(st, ma, mb, p);
+    case 128: return launch_cfg<128, false, false, false, true>(st, ma, mb, p);
+    default: return launch_cfg<256, false, false, false, true>(st, ma, mb, p);
+  }
+}
+
+int gemm_tc(cudaStream_t st, const b200_gemm_desc &d_in, const float *A, const float *B, const float *bias,
             const float *residual, float *Y, void *workspace, size_t workspace_bytes) {
+  b200_gemm_desc d = d_in;
+  if (d.math_mode == B200_MATH_BF16) {
+    if (bf16_qualifies(d)) return gemm_tc_bf16(st, d, A, B, bias, residual, Y, workspace, workspace_bytes);
+    d.math_mode = B200_MATH_TF32;  // batched operands (attention heads addressed in place) keep the TF32 kernels
+  }
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
   const bool pair3 = workspace && aligned16(workspace) && pair3_qualifies(d) &&
                      workspace_bytes >= gemm_tc_workspace_bytes(d);

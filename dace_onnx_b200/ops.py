@@ -12,7 +12,7 @@ from . import _lib
 from ._lib import (ADD, DIV, EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RELU, EPI_BIAS_RESIDUAL, EPI_NONE, EPI_SCALE, ERF,
                    GELU, MATH_MODES, MUL, POW, RELU, SQRT, SUB, AttentionDesc, ConvDesc, GemmDesc, check)  # noqa: F401
 
-default_math_mode = "fp32x3"  # "fp32x3" | "tf32" | "fp32"; overridable per call
+default_math_mode = "fp32x3"  # "fp32x3" | "tf32" | "bf16" | "fp32"; overridable per call
 
 
 def _stream():

@@ -45,6 +45,11 @@ extern "C" {
 #define B200_MATH_FP32X3 0 /* tensor cores, 3xTF32 split (hi*hi + hi*lo + lo*hi), fp32 accumulate: fp32-accurate */
 #define B200_MATH_TF32 1   /* tensor cores, single TF32 pass; ~1e-3 relative error, opt-in */
 #define B200_MATH_FP32 2   /* CUDA-core fp32 FMA kernel; any shape/alignment */
+#define B200_MATH_BF16 3   /* tensor cores, operands rounded to bf16 (8-bit mantissa), fp32 accumulate; ~4e-3 relative
+                              error per product, opt-in. Dense (unbatched) MatMul / Gemm only, through b200_gemm_ws_f32
+                              (both operands are converted into the workspace); batched contractions, the fused
+                              attention and the convolution compute a B200_MATH_BF16 request in TF32, which is more
+                              accurate. */
 
 /* Fused epilogues of the contraction kernels: Y = epi(acc). */
 #define B200_EPI_NONE 0          /* Y = acc */
@@ -114,8 +119,9 @@ B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float
  * from their SDFG init hook (cudnn_implementations.py:281-301). With b200_gemm_workspace_bytes(desc) bytes of
  * 16-byte aligned scratch (0 = this call has no use for one), the fp32-accurate mode (B200_MATH_FP32X3) splits
  * B once into its two TF32 halves there and runs a faster two-CTA kernel; results follow the same 3xTF32
- * arithmetic as b200_gemm_f32. A null or too small workspace is not an error: the call then behaves exactly
- * like b200_gemm_f32. The scratch is only used during the call (stream-ordered). */
+ * arithmetic as b200_gemm_f32. A null or too small workspace is not an error in that mode: the call then behaves
+ * exactly like b200_gemm_f32. B200_MATH_BF16 needs the workspace (it holds the bf16 copies of A and B) and returns
+ * B200_EWORKSPACE without it. The scratch is only used during the call (stream-ordered). */
 B200_API size_t b200_gemm_workspace_bytes(const b200_gemm_desc *desc);
 B200_API int b200_gemm_ws_f32(void *stream, const b200_gemm_desc *desc, const float *A, const float *B,
                               const float *bias, const float *residual, float *Y, void *workspace,

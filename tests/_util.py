@@ -13,6 +13,8 @@ RTOL, ATOL = 1e-4, 1e-5
 REF_RTOL, REF_ATOL = 1e-5, 1e-4
 # Single-pass TF32: operands cut to a 10-bit mantissa by the tensor core; stated wider tolerance.
 TF32_RTOL, TF32_ATOL = 2e-2, 1e-2
+# BF16 operands (8-bit mantissa, round-to-nearest-even), fp32 accumulate; stated wider tolerance.
+BF16_RTOL, BF16_ATOL = 5e-2, 3e-2
 
 
 def golden(name):

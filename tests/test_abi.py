@@ -34,7 +34,7 @@ def test_constants_match_the_header():
     text = open(os.path.join(ROOT, "include", "b200_ops.h")).read()
     consts = {k: int(v.strip("()")) for k, v in re.findall(r"#define\s+(B200_\w+)\s+(\(?-?\d+\)?)", text)}
     assert consts["B200_MATH_FP32X3"] == _lib.MATH_FP32X3 and consts["B200_MATH_TF32"] == _lib.MATH_TF32
-    assert consts["B200_MATH_FP32"] == _lib.MATH_FP32
+    assert consts["B200_MATH_FP32"] == _lib.MATH_FP32 and consts["B200_MATH_BF16"] == _lib.MATH_BF16
     assert [consts[k] for k in ("B200_EPI_NONE", "B200_EPI_BIAS", "B200_EPI_BIAS_RELU", "B200_EPI_BIAS_GELU",
                                 "B200_EPI_BIAS_RESIDUAL", "B200_EPI_SCALE")] == list(range(6))
     assert [consts[k] for k in ("B200_ADD", "B200_SUB", "B200_MUL", "B200_DIV", "B200_POW")] == list(range(5))

@@ -109,6 +109,8 @@ def test_math_mode_env(monkeypatch):
     monkeypatch.setenv(impl.MATH_MODE_ENV, "tf32")
     assert impl.math_mode() == 1
     monkeypatch.setenv(impl.MATH_MODE_ENV, "bf16")
+    assert impl.math_mode() == 3
+    monkeypatch.setenv(impl.MATH_MODE_ENV, "fp64")
     with pytest.raises(ValueError):
         impl.math_mode()
 
