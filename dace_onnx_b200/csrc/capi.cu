@@ -3,6 +3,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "contract.cuh"
 #include "tc_common.cuh"
@@ -31,15 +33,19 @@ __device__ unsigned g_device_status = 0;
 
 unsigned *device_status_ptr() {
   constexpr int kMaxDevices = 64;
-  static unsigned *cache[kMaxDevices] = {};  // address of the symbol on each device; never changes
+  // address of the symbol on each device; never changes. Atomic, so that host threads making their first calls
+  // concurrently race benignly (they store the same value).
+  static std::atomic<unsigned *> cache[kMaxDevices];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-  if (!cache[dev]) {
+  unsigned *p = cache[dev].load(std::memory_order_relaxed);
+  if (!p) {
     void *ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
-    cache[dev] = static_cast<unsigned *>(ptr);
+    p = static_cast<unsigned *>(ptr);
+    cache[dev].store(p, std::memory_order_relaxed);
   }
-  return cache[dev];
+  return p;
 }
 
 // Self-test of the bounded wait every tensor-core kernel uses: one CTA, one mbarrier that nothing ever arrives at,

@@ -16,9 +16,9 @@
 //     the L2 -> shared-memory path KW times instead of KH * KW times (that path, not the tensor pipe, bounded a
 //     version with one load per tap). Out-of-range coordinates are zero-filled by the TMA unit, which is the
 //     zero padding. Two threads take turns issuing these loads (even / odd stages);
-//   * two threads of the even CTA issue the MMAs, each the k-steps of one half of every k-block into its own
-//     TMEM accumulator (one thread alone cannot issue N = 64 instructions as fast as the pipe retires them);
-//     the epilogue adds the two accumulators;
+//   * four threads (two in 3xTF32 mode) of the even CTA issue the MMAs, each its share of the k-steps of every
+//     k-block into its own TMEM accumulators (one thread alone cannot issue N = 64 instructions as fast as the
+//     pipe retires them); the epilogue adds the accumulators;
 //   * 3xTF32 mode: eight split warps (two groups on alternate k-blocks) turn the landed rows into
 //     hi = tf32(x) and lo = tf32(x - hi) halves in TMEM (the MMAs read A from TMEM, B_hi / B_lo from the
 //     resident filter) and run lo*hi + hi*lo + hi*hi;
@@ -84,8 +84,16 @@ template <bool SPLIT3>
 struct PairCfg {
   static constexpr int kEpilogueWarp0 = 4, kEpilogueWarps = 8;
   static constexpr int kSplitWarp0 = kEpilogueWarp0 + kEpilogueWarps, kSplitWarps = SPLIT3 ? 8 : 0;
-  static constexpr int kThreads = 32 * (kSplitWarp0 + kSplitWarps);
-  static constexpr int kTmemCols = SPLIT3 ? 512 : 256;  // 4 accumulators (+ 4 A slots)
+  // Threads that issue MMAs (even CTA): warps 1 and 2, and in TF32 mode two more warps behind the epilogue warps.
+  // Issuer i takes k-steps i * (4 / kIssuers) ... of every k-block into accumulators 2i and 2i + 1. One thread issues
+  // an MMA every ~100 cycles and pays several hundred per barrier wait / commit, which for N = 64 instructions
+  // (32 cycles of tensor work each) is the kernel's limit: four threads in TF32 mode (all 512 TMEM columns are
+  // accumulators), two in 3xTF32 mode (half of TMEM holds A's hi / lo halves).
+  static constexpr int kIssuers = SPLIT3 ? 2 : 4;
+  static constexpr int kStepsPerIssuer = (BK / UMMA_K) / kIssuers;
+  static constexpr int kExtraIssuerWarp0 = kSplitWarp0 + kSplitWarps;
+  static constexpr int kThreads = 32 * (kExtraIssuerWarp0 + (kIssuers > 2 ? kIssuers - 2 : 0));
+  static constexpr int kTmemCols = 512;  // 2 accumulators per issuer (+ 4 A slots in 3xTF32 mode)
   static constexpr int kSlotCol0 = 4 * kAccCols;
 };
 
@@ -100,14 +108,14 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const int stage_bytes = p.kbs * p.slab_bytes;
   uint8_t *stages = smem + b_bytes;
   uint64_t *bars = reinterpret_cast<uint64_t *>(stages + (size_t)p.stages * stage_bytes);
-  // full[8] empty[8] split[4] slotfree[4] tfull[4] tempty[4] bfull
+  // full[8] empty[8] split[4] slotfree[4] tfull[8] tempty[8] bfull
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_split = bar_empty + 8 * kMaxStages;
   const uint32_t bar_slotfree = bar_split + 8 * kSlots;
   const uint32_t bar_tfull = bar_slotfree + 8 * kSlots;
-  const uint32_t bar_tempty = bar_tfull + 8 * 4;
-  const uint32_t bar_bfull = bar_tempty + 8 * 4;
+  const uint32_t bar_tempty = bar_tfull + 8 * 8;
+  const uint32_t bar_bfull = bar_tempty + 8 * 8;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ __align__(16) float s_bias[kAccCols];
@@ -123,14 +131,14 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     s_abort = 0;
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
-      // stage release: the two issuing threads' commits (TF32) or this CTA's split warps (3xTF32)
-      mbar_init(bar_empty + 8 * s, SPLIT3 ? C::kSplitWarps : 2);
+      // stage release: the issuing threads' commits (TF32) or this CTA's split warps (3xTF32)
+      mbar_init(bar_empty + 8 * s, SPLIT3 ? C::kSplitWarps : C::kIssuers);
     }
     for (int t = 0; t < kSlots; ++t) {
       mbar_init(bar_split + 8 * t, 2 * 4);  // one arrival per split warp of one group, both CTAs
-      mbar_init(bar_slotfree + 8 * t, 2);   // both issuing threads' commits
+      mbar_init(bar_slotfree + 8 * t, C::kIssuers);  // the issuing threads' commits
     }
-    for (int a = 0; a < 4; ++a) {
+    for (int a = 0; a < 2 * C::kIssuers; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps);  // one arrival per epilogue warp of both CTAs
     }
@@ -205,15 +213,16 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 || warp == 2) {
+  } else if (warp == 1 || warp == 2 || warp >= C::kExtraIssuerWarp0) {
     // ------------------------------- MMA issuers (even CTA) -------------------------------
-    // Issuer i runs k-steps 2i and 2i+1 of every k-block into its own accumulators (buffers 2i, 2i+1).
+    // Issuer i runs its k-steps of every k-block into its own accumulators (buffers 2i, 2i+1).
     if (lane == 0 && rank == 0) {
-      const int i = warp - 1;
+      const int i = warp <= 2 ? warp - 1 : 2 + (warp - C::kExtraIssuerWarp0);
+      constexpr int kSteps = C::kStepsPerIssuer;
       const uint32_t idesc = make_idesc_pair(p.bn, false);
       constexpr uint32_t kStep = (UMMA_K * 4) >> 4;  // 32 bytes inside the swizzle row
-      const uint64_t a_desc0 = make_smem_desc(stage_base, 16, 1024, kLayoutSw128) + (uint32_t)(2 * i) * kStep;
-      const uint64_t b_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128) + (uint32_t)(2 * i) * kStep;
+      const uint64_t a_desc0 = make_smem_desc(stage_base, 16, 1024, kLayoutSw128) + (uint32_t)(kSteps * i) * kStep;
+      const uint64_t b_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128) + (uint32_t)(kSteps * i) * kStep;
       const uint32_t b_kb16 = (uint32_t)p.b_kb_bytes >> 4;
       const uint32_t b_lo16 = (uint32_t)(p.bn / 2 * 128) >> 4;
       const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
@@ -254,9 +263,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 const uint32_t first = n % kChunkKb ? 1u : 0u;
                 if (!(ok = mbar_wait(bar_split + 8 * slot, slot_ph, abort_flag, p.status, 4u))) break;
                 tc_fence_after();
-                const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)slot * 64 + (uint32_t)(2 * i) * UMMA_K;
+                const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)slot * 64 + (uint32_t)(kSteps * i) * UMMA_K;
 #pragma unroll
-                for (int j = 0; j < 2; ++j) {
+                for (int j = 0; j < kSteps; ++j) {
                   umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K + 32, b_d + j * kStep, idesc, j > 0 ? 1u : first);  // lo * hi
                   umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + b_lo16 + j * kStep, idesc, 1u);              // hi * lo
                   umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + j * kStep, idesc, 1u);                       // hi * hi
@@ -267,7 +276,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 // rows [8 kh, 8 kh + 128) of channel block q of the slab: kh image rows = kh * 1024 bytes down
                 const uint64_t a_d = a_desc0 + (uint32_t)s * stage16 + (uint32_t)q * slab16 + (uint32_t)kh * (1024 >> 4);
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < kSteps; ++j)
                   umma_tf32_pair(d_tmem, a_d + j * kStep, b_d + j * kStep, idesc, (j > 0 || n > 0) ? 1u : 0u);
               }
             }
@@ -301,27 +310,32 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
       for (int j = 0; j < 32; ++j) sum[j] = 0.f;
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += chunk) {
-        if (!(ok = mbar_wait(bar_tfull + 8 * buf, buf_ph, abort_flag, p.status, 8u))) break;
-        if (!(ok = mbar_wait(bar_tfull + 8 * (2 + buf), buf_ph, abort_flag, p.status, 8u))) break;
+#pragma unroll
+        for (int i = 0; i < C::kIssuers; ++i)
+          if (ok) ok = mbar_wait(bar_tfull + 8 * (2 * i + buf), buf_ph, abort_flag, p.status, 8u);
+        if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 32; c += 16) {
-          uint32_t v0[16], v1[16];
-          tmem_ld16(lane_addr + (uint32_t)(buf * kAccCols + c), v0);
-          tmem_ld16(lane_addr + (uint32_t)((2 + buf) * kAccCols + c), v1);
+          uint32_t v[C::kIssuers][16];
+#pragma unroll
+          for (int i = 0; i < C::kIssuers; ++i) tmem_ld16(lane_addr + (uint32_t)((2 * i + buf) * kAccCols + c), v[i]);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) sum[c + j] += __uint_as_float(v0[j]) + __uint_as_float(v1[j]);
+          for (int j = 0; j < 16; ++j) {
+            float t = __uint_as_float(v[0][j]);
+#pragma unroll
+            for (int i = 1; i < C::kIssuers; ++i) t += __uint_as_float(v[i][j]);
+            sum[c + j] += t;
+          }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          if (rank == 0) {
-            mbar_arrive(bar_tempty + 8 * buf);
-            mbar_arrive(bar_tempty + 8 * (2 + buf));
-          } else {
-            mbar_arrive_cluster_relaxed(tempty0 + 8 * buf);
-            mbar_arrive_cluster_relaxed(tempty0 + 8 * (2 + buf));
+#pragma unroll
+          for (int i = 0; i < C::kIssuers; ++i) {
+            if (rank == 0) mbar_arrive(bar_tempty + 8 * (2 * i + buf));
+            else mbar_arrive_cluster_relaxed(tempty0 + 8 * (2 * i + buf));
           }
         }
         if (++buf == 2) { buf = 0; buf_ph ^= 1; }

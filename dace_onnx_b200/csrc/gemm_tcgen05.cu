@@ -20,6 +20,9 @@
 // status word, all roles leave their loops, TMEM is released and the kernel returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <string.h>
+
+#include <atomic>
 
 #include "common.cuh"
 #include "contract.cuh"
@@ -1066,12 +1069,25 @@ void batch_axis(int64_t extent, int64_t stride_elems, uint64_t fallback_bytes, u
   }
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per (function, device) and sticks: do it once each.
+// `done` is the caller's per-kernel flag word (bit d: set on device d).
+template <typename Kernel>
+int raise_dynamic_smem_once(Kernel kern, int bytes, const char *what, std::atomic<uint64_t> &done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ECUDA, "%s: bad device", what);
+  if (done.load(std::memory_order_relaxed) >> dev & 1) return B200_OK;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    return fail(B200_ECUDA, "%s: cannot set dynamic shared memory to %d", what, bytes);
+  done.fetch_or(1ull << dev, std::memory_order_relaxed);
+  return B200_OK;
+}
+
 template <int BN, bool B_MN, bool SPLIT3, bool CONV = false, bool BF16 = false>
 int launch_cfg(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   using C = Cfg<BN, SPLIT3>;
   auto kern = gemm_tc_kernel<BN, B_MN, SPLIT3, CONV, BF16>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-    return fail(B200_ECUDA, "gemm(tc): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  static std::atomic<uint64_t> smem_set{0};  // one per kernel instantiation
+  if (int rc = raise_dynamic_smem_once(kern, C::kSmemBytes, "gemm(tc)", smem_set)) return rc;
   const int64_t grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
   kern<<<(unsigned)grid, C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_tc");
@@ -1081,14 +1097,14 @@ template <int BN, bool B_MN, bool BF16 = false>
 int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, GemmParams &p) {
   using C = Cfg2<BN>;
   auto kern = gemm_tc_pair_kernel<BN, B_MN, BF16>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-    return fail(B200_ECUDA, "gemm(tc pair): cannot set dynamic shared memory to %d", C::kSmemBytes);
+  static std::atomic<uint64_t> smem_set{0};  // one per kernel instantiation
+  if (int rc = raise_dynamic_smem_once(kern, C::kSmemBytes, "gemm(tc pair)", smem_set)) return rc;
   // A persistent grid must not exceed the clusters the device can hold at once (both CTAs of a
   // pair sit in one GPC, so this is fewer than SMs / 2); extra clusters would run a second wave alone.
-  static int max_pairs[64] = {};  // per device; the answer depends only on the kernel and its resources
+  static std::atomic<int> max_pairs[64];  // per device (zero-initialised); depends only on the kernel and its resources
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ECUDA, "gemm(tc pair): bad device");
-  if (max_pairs[dev] == 0) {
+  if (max_pairs[dev].load(std::memory_order_relaxed) == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kNumSMs, 1, 1);
     cfg.blockDim = dim3(C::kThreads, 1, 1);
@@ -1103,10 +1119,11 @@ int launch_pair(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mb, G
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1)
       return fail(B200_ECUDA, "gemm(tc pair): cudaOccupancyMaxActiveClusters failed");
-    max_pairs[dev] = n;
+    max_pairs[dev].store(n, std::memory_order_relaxed);
   }
   const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles * p.num_tiles_batch;
-  const int64_t pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+  const int64_t cap = max_pairs[dev].load(std::memory_order_relaxed);
+  const int64_t pairs = tiles < cap ? tiles : cap;
   kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_tc_pair");
 }
@@ -1115,12 +1132,12 @@ template <int BN, bool B_MN>
 int launch_pair3(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mbh, const CUtensorMap &mbl, GemmParams &p) {
   using C = Cfg3P<BN>;
   auto kern = gemm_tc_pair3_kernel<BN, B_MN>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
-    return fail(B200_ECUDA, "gemm(tc pair3): cannot set dynamic shared memory to %d", C::kSmemBytes);
-  static int max_pairs[64] = {};  // per device, as in launch_pair
+  static std::atomic<uint64_t> smem_set{0};  // one per kernel instantiation
+  if (int rc = raise_dynamic_smem_once(kern, C::kSmemBytes, "gemm(tc pair3)", smem_set)) return rc;
+  static std::atomic<int> max_pairs[64];  // per device, as in launch_pair
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200_ECUDA, "gemm(tc pair3): bad device");
-  if (max_pairs[dev] == 0) {
+  if (max_pairs[dev].load(std::memory_order_relaxed) == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kNumSMs, 1, 1);
     cfg.blockDim = dim3(C::kThreads, 1, 1);
@@ -1135,10 +1152,11 @@ int launch_pair3(cudaStream_t st, const CUtensorMap &ma, const CUtensorMap &mbh,
     int n = 0;
     if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1)
       return fail(B200_ECUDA, "gemm(tc pair3): cudaOccupancyMaxActiveClusters failed");
-    max_pairs[dev] = n;
+    max_pairs[dev].store(n, std::memory_order_relaxed);
   }
   const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
-  const int64_t pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+  const int64_t cap = max_pairs[dev].load(std::memory_order_relaxed);
+  const int64_t pairs = tiles < cap ? tiles : cap;
   kern<<<(unsigned)(2 * pairs), C::kThreads, C::kSmemBytes, st>>>(ma, mbh, mbl, p);
   return check_launch("gemm_tc_pair3");
 }
@@ -1225,7 +1243,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;  // process-wide driver entry point; identical for every device
+  static std::atomic<EncodeTiledFn> cached{nullptr};  // process-wide driver entry point; identical for every device
+  EncodeTiledFn fn = cached.load(std::memory_order_relaxed);
   if (!fn) {
     void *ptr = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -1233,12 +1252,47 @@ static EncodeTiledFn get_encode_fn() {
         q != cudaDriverEntryPointSuccess)
       return nullptr;
     fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    cached.store(fn, std::memory_order_relaxed);
   }
   return fn;
 }
 
+// A caller with static shapes (a DaCe tasklet, a planned ONNX graph, a CUDA-graph capture) asks for the same
+// tensor maps on every call. Each host thread keeps the last maps it encoded in a small direct-mapped table keyed by
+// everything the encoding depends on (base address, extents, strides, box, swizzle); a hit is a 128-byte copy
+// instead of a driver call. The table holds descriptors, never device memory.
+namespace {
+struct MapKey {
+  const void *base;
+  uint64_t dims[4], strides[3];
+  uint32_t box[3], swizzle;
+  bool operator==(const MapKey &o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapSlot {
+  bool valid = false;
+  MapKey key;
+  CUtensorMap map;
+};
+constexpr int kMapSlots = 64;
+}  // namespace
+
 int tc::encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], const uint64_t strides_bytes[3],
                uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle, uint32_t box2) {
+  static thread_local MapSlot table[kMapSlots];
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  for (int i = 0; i < 4; ++i) key.dims[i] = dims[i];
+  for (int i = 0; i < 3; ++i) key.strides[i] = strides_bytes[i];
+  key.box[0] = box0; key.box[1] = box1; key.box[2] = box2;
+  key.swizzle = (uint32_t)swizzle;
+  uint64_t h = reinterpret_cast<uintptr_t>(base) * 0x9E3779B97F4A7C15ull;
+  h ^= (dims[0] * 31 + dims[1]) * 0xC2B2AE3D27D4EB4Full + strides_bytes[0] * 131 + box0 * 7 + box1 * 3 + box2 + (uint64_t)swizzle;
+  MapSlot &slot = table[(h >> 20) % kMapSlots];
+  if (slot.valid && slot.key == key) {
+    *map = slot.map;
+    return B200_OK;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(B200_ECUDA, "cuTensorMapEncodeTiled entry point not available");
   cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
@@ -1254,6 +1308,9 @@ int tc::encode_map(CUtensorMap *map, const float *base, const uint64_t dims[4], 
                 (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
                 (unsigned long long)dims[3], (unsigned long long)strides_bytes[0],
                 (unsigned long long)strides_bytes[1], (unsigned long long)strides_bytes[2], box0, box1);
+  slot.valid = true;
+  slot.key = key;
+  slot.map = *map;
   return B200_OK;
 }
 
