@@ -9,13 +9,16 @@
 // of Q K^T, V as the MN-major B operand of P V), so loads run ahead of the MMAs across tiles and
 // heads. Per query tile:
 //   warp 0 loads Q, the key blocks and the value blocks                      (cp.async.bulk.tensor)
-//   warp 1 issues Q K^T block by block into TMEM columns [0, S)  (tcgen05.mma kind::tf32, A and B in smem)
+//   warps 1 and 10 issue Q K^T block by block into TMEM columns [0, S)  (tcgen05.mma kind::tf32, A and B in
+//             smem): warp 1 the even key blocks, warp 10 the odd ones
 //   warps 2-9 (two per score row, alternating 32-column blocks) read the row from TMEM, take its
 //             maximum, overwrite it in place with P = exp2((s - max) * scale * log2 e) and sum P
 //             (tcgen05.ld / st)
-//   warp 1 issues P V with the A operand read from TMEM into columns [448, 512), 128 key columns
-//             at a time as soon as the softmax warps have published them
-//   warps 2-9 read the 64 output columns, divide by the row sum and store [row, head*64 .. +64).
+//   warps 1 and 10 issue P V with the A operand read from TMEM, 128 key columns at a time as soon as the softmax
+//             warps have published them: warp 1 the first 64 keys of a group into columns [384, 448), warp 10
+//             the rest into [448, 512). (One thread issues an MMA every ~100 clk, and the 48 N = 64 products of a
+//             tile were the longest phase; two threads on two accumulators halve it.)
+//   warps 2-9 add the two partial outputs, divide by the row sum and store [row, head*64 .. +64).
 // HBM traffic is Q, K, V once and the context once: 16 B per (token, head-dim element) instead of
 // the 4 * S * S * 4 B per head the unfused chain moves.
 //
@@ -32,9 +35,10 @@ namespace {
 constexpr int kD = 64;                  // head dimension
 constexpr int kBlkBytes = 128 * kD * 4; // 32 KiB: 128 rows x 64 fp32 as two slices of [128 rows][128 B]
 constexpr int kRing = 5;                // K / V blocks in flight (shared memory: (2 + kRing) x 32 KiB)
-constexpr int kOCol = 448;              // TMEM column of the output accumulator
+constexpr int kOCol = 384;              // TMEM columns of the two partial output accumulators: [384, 448), [448, 512)
+constexpr int kOCol2 = 448;
 constexpr int kMaxS = 384;
-constexpr int kThreads = 32 * (2 + 8);   // producer, MMA issuer, 8 softmax / output warps
+constexpr int kThreads = 32 * (2 + 8 + 1);   // producer, MMA issuer, 8 softmax / output warps, second MMA issuer
 
 struct AttnParams {
   int S;              // sequence length
@@ -66,16 +70,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     s_abort = 0;
+    // barriers the two issuing threads signal together take two arrivals
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_q_full + 8 * i, 1);
-      mbar_init(bar_q_empty + 8 * i, 1);
+      mbar_init(bar_q_empty + 8 * i, 2);
     }
     for (int i = 0; i < kRing; ++i) {
       mbar_init(bar_ring_full + 8 * i, 1);
-      mbar_init(bar_ring_empty + 8 * i, 1);
+      mbar_init(bar_ring_empty + 8 * i, 2);
     }
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_o_full, 1);
+    mbar_init(bar_s_full, 2);
+    mbar_init(bar_o_full, 2);
     mbar_init(bar_o_empty, 256);
     for (int c = 0; c < 4; ++c) mbar_init(bar_p_full + 8 * c, 256);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -123,47 +128,56 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------- MMA issuers -------------------------------
+    // Both threads walk the same sequence of ring slots; `second` decides which score blocks and which half of
+    // every P V group are this thread's. A key block is released by its one consumer with two commits, a value
+    // block by one commit of each thread (every ring barrier takes two arrivals).
     if (lane == 0) {
+      const int second = warp == 10 ? 1 : 0;
       int rs = 0, qs = 0;
       uint32_t r_ph = 0, q_ph = 0, t_ph = 0;  // t_ph: phase of the per-tile barriers (o_empty, p_full, o_full)
       // Descriptors are built once; inside the loops an MMA costs one 64-bit add on its operand
-      // descriptors (the start-address field counts 16-byte units), because this single thread's
+      // descriptors (the start-address field counts 16-byte units), because the issuing thread's
       // instruction latency, not the tensor core, would otherwise bound the small MMAs.
       const uint32_t idesc_o = make_idesc(kD, true);
       const uint32_t idesc_full = make_idesc(128, false);
       const uint64_t kdesc0 = make_smem_desc(0, 16, 1024, kLayoutSw128);                    // Q and K blocks
       const uint64_t vdesc0 = make_smem_desc(0, kBlkBytes / 2, 512, kLayoutSw128Base32);   // V blocks
+      const uint32_t o_tmem = tmem_base + (second ? kOCol2 : kOCol);
       bool ok = true;
       for (int64_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
         for (int mt = 0; mt < p.n_blocks && ok; ++mt) {
           if (!(ok = mbar_wait(bar_q_full + 8 * qs, q_ph, abort_flag, p.status, 2u))) break;
           const uint64_t a_base = kdesc0 + ((q_smem + qs * kBlkBytes) >> 4);
-          // S[:, 128 j .. ] = Q K_j^T, one key block at a time as it lands
+          // S[:, 128 j .. ] = Q K_j^T, one key block at a time as it lands; block j belongs to thread j % 2
           for (int j = 0; j < p.n_blocks && ok; ++j) {
-            if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 2u))) break;
-            tc_fence_after();
-            const int n_len = p.S - j * 128;
-            const uint32_t idesc_s = n_len >= 128 ? idesc_full : make_idesc(n_len, false);
-            const uint64_t b_base = kdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
-            const uint32_t d_tmem = tmem_base + j * 128;
+            if ((j & 1) == second) {
+              if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 2u))) break;
+              tc_fence_after();
+              const int n_len = p.S - j * 128;
+              const uint32_t idesc_s = n_len >= 128 ? idesc_full : make_idesc(n_len, false);
+              const uint64_t b_base = kdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
+              const uint32_t d_tmem = tmem_base + j * 128;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              // k-block kb = ks / 4 is half a block further (kBlkBytes / 2), k-step kk = ks % 4 is 32 B further
-              constexpr uint32_t kHalf = (kBlkBytes / 2) >> 4;
-              const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 2;
-              umma_tf32(d_tmem, a_base + off, b_base + off, idesc_s, ks > 0 ? 1u : 0u);
+              for (int ks = 0; ks < 8; ++ks) {
+                // k-block kb = ks / 4 is half a block further (kBlkBytes / 2), k-step kk = ks % 4 is 32 B further
+                constexpr uint32_t kHalf = (kBlkBytes / 2) >> 4;
+                const uint32_t off = (ks >> 2) * kHalf + (ks & 3) * 2;
+                umma_tf32(d_tmem, a_base + off, b_base + off, idesc_s, ks > 0 ? 1u : 0u);
+              }
+              umma_commit(bar_ring_empty + 8 * rs);
+              umma_commit(bar_ring_empty + 8 * rs);
             }
-            umma_commit(bar_ring_empty + 8 * rs);
             if (++rs == kRing) { rs = 0; r_ph ^= 1; }
           }
           if (!ok) break;
-          umma_commit(bar_q_empty + 8 * qs);  // Q buffer reusable
-          umma_commit(bar_s_full);            // scores ready for the softmax warps
+          umma_commit(bar_q_empty + 8 * qs);  // Q buffer reusable once both threads' products have read it
+          umma_commit(bar_s_full);            // scores ready for the softmax warps (both threads' blocks)
           if (++qs == 2) { qs = 0; q_ph ^= 1; }
           // O = P V, A operand (P) from TMEM; the previous tile's O must have been read out
           if (!(ok = mbar_wait(bar_o_empty, t_ph ^ 1, abort_flag, p.status, 2u))) break;
+          uint32_t started = 0;  // 0 until this thread's accumulator has received its first product of the tile
           for (int c = 0; c < n_chunks && ok; ++c) {
             if (!(ok = mbar_wait(bar_p_full + 8 * c, t_ph, abort_flag, p.status, 4u))) break;
             if (!(ok = mbar_wait(bar_ring_full + 8 * rs, r_ph, abort_flag, p.status, 4u))) break;
@@ -171,21 +185,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const uint64_t v_base = vdesc0 + ((ring_smem + rs * kBlkBytes) >> 4);
             const uint32_t p_tmem = tmem_base + c * 128;
             const int k_len = p.S - c * 128 < 128 ? p.S - c * 128 : 128;
-            // 8 key rows of V (8 x 128 B = 64 descriptor units) and 8 columns of P per MMA
-            if (k_len == 128) {
+            // 8 key rows of V (8 x 128 B = 64 descriptor units) and 8 columns of P per MMA; this thread's keys
+            // are [0, 64) or [64, 128) of the group
+            const int k8_lo = second ? 8 : 0, k8_hi = second ? k_len / 8 : (k_len / 8 < 8 ? k_len / 8 : 8);
+            if (k8_hi - k8_lo == 8) {
 #pragma unroll
-              for (int k8 = 0; k8 < 16; ++k8)
-                umma_tf32_ts(tmem_base + kOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (c > 0 || k8 > 0) ? 1u : 0u);
+              for (int q = 0; q < 8; ++q) {
+                const int k8 = k8_lo + q;
+                umma_tf32_ts(o_tmem, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, q > 0 ? 1u : started);
+              }
+              started = 1;
             } else {
-              for (int k8 = 0; k8 * 8 < k_len; ++k8)
-                umma_tf32_ts(tmem_base + kOCol, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, (c > 0 || k8 > 0) ? 1u : 0u);
+              for (int k8 = k8_lo; k8 < k8_hi; ++k8) {
+                umma_tf32_ts(o_tmem, p_tmem + k8 * 8, v_base + k8 * 64, idesc_o, started);
+                started = 1;
+              }
             }
             umma_commit(bar_ring_empty + 8 * rs);
             if (++rs == kRing) { rs = 0; r_ph ^= 1; }
           }
           if (!ok) break;
           umma_commit(bar_o_full);
-          // P lives where the next tile's scores go: wait until the P V MMAs have consumed it
+          // P lives where the next tile's scores go: wait until both threads' P V MMAs have consumed it
           if (!(ok = mbar_wait(bar_o_full, t_ph, abort_flag, p.status, 2u))) break;
           t_ph ^= 1;
         }
@@ -254,9 +275,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         {
           uint32_t v[32];
           tmem_ld32(lane_addr + kOCol + half * 32, v);
+          if (p.S > 64) {  // the second partial output exists once a key group has more than 64 keys
+            uint32_t v2[32];
+            tmem_ld32(lane_addr + kOCol2 + half * 32, v2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v2[j]));
+          }
           tmem_ld_wait();
           tc_fence_before();
-          mbar_arrive(bar_o_empty);  // the accumulator may be overwritten by the next tile
+          mbar_arrive(bar_o_empty);  // the accumulators may be overwritten by the next tile
           if (row < p.S) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
