@@ -235,6 +235,11 @@ def test_math_mode_flag_is_read_at_expansion(plugin, monkeypatch):
     node, state, sdfg = place(ns, name, "mm", descs, ins, outs, **attrs)
     code = impl.forward(node, state, sdfg).states[0].tasklets[0].code
     assert "b200_gemm_f32(" in code and code.split("1.0f, ")[1].startswith("1}")     # math_mode 1, no workspace
+    monkeypatch.setenv("B200_MATH_MODE", "bf16")       # bf16 keeps its operand copies in a workspace of the SDFG state
+    node, state, sdfg = place(ns, name, "mm", descs, ins, outs, **attrs)
+    code = impl.forward(node, state, sdfg).states[0].tasklets[0].code
+    assert "b200_gemm_ws_f32(" in code and code.split("1.0f, ")[1].startswith("3}")
+    assert "b200_gemm_workspace_bytes" in impl.environments[0].init_code
     monkeypatch.setenv("B200_MATH_MODE", "fp64")
     with pytest.raises(ValueError):
         impl.forward(node, state, sdfg)
