@@ -552,7 +552,7 @@ def kernel_cases(device):
         "gemm_fp32x3_ffn1_no_workspace": gemm_no_workspace(16384, 3072, 768, "fp32x3", EPI_BIAS_GELU),
         "attn_qk_tf32": attn_qk(32, 16, 384, 64, "tf32"), "attn_pv_tf32": attn_pv(32, 16, 384, 64, "tf32"),
         "attention_fused_tf32": attn_fused(32, 16, 384, 64),
-        "attention_stream_tf32_s512": attn_fused(64, 12, 512, 64), "attention_stream_tf32_s2048": attn_fused(8, 16, 2048, 64),
+        "attention_fused_tf32_s512": attn_fused(64, 12, 512, 64), "attention_fused_tf32_s2048": attn_fused(8, 16, 2048, 64),
         "attention_fused_tf32_headmajor": attn_fused_headmajor(32, 16, 384, 64),
     }
 

@@ -47,7 +47,7 @@ constexpr int A_STAGE_BYTES = BM * BK * 4;  // 16 KiB
 constexpr int kMaxStages = 8;
 constexpr int kSlots = 4;                   // TMEM slots for A's hi / lo halves (3xTF32), 64 columns each
 constexpr int kAccCols = 64;                // columns per accumulator
-constexpr int kChunkKb = 8;                 // 3xTF32: k-blocks per accumulation chunk (each issuer adds 128 values of K)
+constexpr int kMaxChunkKb = 20;             // 3xTF32: most k-blocks per accumulation chunk (60 products per accumulator)
 constexpr int kBarrierBytes = 512;
 constexpr int kMaxDynamicSmem = 227 * 1024 - 1024;  // the rest of the 227 KiB is the kernel's static shared memory
 
@@ -57,6 +57,7 @@ struct ConvPairParams {
   int slab_bytes;              // one channel block of a stage: (16 + KH - 1) image rows x 8 pixels x 128 bytes
   int tiles_w, tiles_per_img;  // 8 x 16 pixel tiles per row of tiles / per image
   int cblocks, num_kb;
+  int chunk_kb;           // 3xTF32: k-blocks summed in one accumulator before the epilogue warps take it over
   int kbs;                // 32-channel blocks per stage: 2, or 1 when the input has at most 32 channels
   int groups;             // stages per filter column
   int stages_per_tile;    // KW * groups
@@ -84,18 +85,34 @@ template <bool SPLIT3>
 struct PairCfg {
   static constexpr int kEpilogueWarp0 = 4, kEpilogueWarps = 8;
   static constexpr int kSplitWarp0 = kEpilogueWarp0 + kEpilogueWarps, kSplitWarps = SPLIT3 ? 8 : 0;
-  // Threads that issue MMAs (even CTA): warps 1 and 2, and in TF32 mode two more warps behind the epilogue warps.
-  // Issuer i takes k-steps i * (4 / kIssuers) ... of every k-block into accumulators 2i and 2i + 1. One thread issues
-  // an MMA every ~100 cycles and pays several hundred per barrier wait / commit, which for N = 64 instructions
-  // (32 cycles of tensor work each) is the kernel's limit: four threads in TF32 mode (all 512 TMEM columns are
-  // accumulators), two in 3xTF32 mode (half of TMEM holds A's hi / lo halves).
-  static constexpr int kIssuers = SPLIT3 ? 2 : 4;
-  static constexpr int kStepsPerIssuer = (BK / UMMA_K) / kIssuers;
+  // Threads that issue MMAs (even CTA): four, in warps of their own. One thread issues a tcgen05.mma every ~55
+  // cycles at best, and every barrier wait in between costs it ~200 more (measured), while an N = 64 pair
+  // instruction occupies the tensor pipe for ~53 cycles with A in shared memory and ~36 with A in TMEM.
+  //   TF32:   issuer i takes k-step i of every k-block into two accumulators of its own (all 512 TMEM columns);
+  //           it waits and commits once per stage.
+  //   3xTF32: A's hi / lo halves come through four 64-column TMEM slots, one k-block each. Issuer i owns slot i,
+  //           i.e. the k-blocks whose running number is i modulo 4, and issues all twelve products of such a
+  //           k-block (one wait and one commit per twelve MMAs) into its one accumulator; the other half of TMEM
+  //           holds the slots, so an issuer waits for the epilogue warps at every chunk boundary.
+  static constexpr int kIssuers = 4;
+  static constexpr int kBufs = SPLIT3 ? 1 : 2;
+  static constexpr int kStepsPerIssuer = SPLIT3 ? BK / UMMA_K : (BK / UMMA_K) / kIssuers;
   static constexpr int kExtraIssuerWarp0 = kSplitWarp0 + kSplitWarps;
-  static constexpr int kThreads = 32 * (kExtraIssuerWarp0 + (kIssuers > 2 ? kIssuers - 2 : 0));
-  static constexpr int kTmemCols = 512;  // 2 accumulators per issuer (+ 4 A slots in 3xTF32 mode)
+  // 3xTF32 runs three times longer per stage: one TMA producer is enough there and warp 3 issues MMAs instead
+  static constexpr int kProducers = SPLIT3 ? 1 : 2;
+  static constexpr int kLowIssuers = 4 - kProducers;  // issuers among warps 1..3
+  static constexpr int kThreads = 32 * (kExtraIssuerWarp0 + kIssuers - kLowIssuers);
+  static constexpr int kTmemCols = 512;  // kBufs accumulators per issuer (+ 4 A slots in 3xTF32 mode)
   static constexpr int kSlotCol0 = 4 * kAccCols;
 };
+
+// Round an fp32 value to TF32 precision (nearest, ties away from zero: what cvt.rna.tf32.f32 computes) with two
+// full-rate integer instructions instead of the slower conversion instruction; the split warps convert 64 values
+// per thread and k-block.
+__device__ __forceinline__ uint32_t split_hi(float x) { return (__float_as_uint(x) + 0x1000u) & 0xffffe000u; }
+
+// 3xTF32: does issuer i (owner of the k-blocks whose running number is i modulo 4) own a k-block in [lo, hi)?
+__device__ __forceinline__ bool chunk_has(int i, int64_t lo, int64_t hi) { return lo + ((i - (int)(lo & 3)) & 3) < hi; }
 
 template <bool SPLIT3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<SPLIT3>::kThreads, 1)
@@ -136,9 +153,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     for (int t = 0; t < kSlots; ++t) {
       mbar_init(bar_split + 8 * t, 2 * 4);  // one arrival per split warp of one group, both CTAs
-      mbar_init(bar_slotfree + 8 * t, C::kIssuers);  // the issuing threads' commits
+      mbar_init(bar_slotfree + 8 * t, 1);    // the commit of the issuing thread that owns the slot
     }
-    for (int a = 0; a < 2 * C::kIssuers; ++a) {
+    for (int a = 0; a < C::kBufs * C::kIssuers; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 2 * C::kEpilogueWarps);  // one arrival per epilogue warp of both CTAs
     }
@@ -157,10 +174,10 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const uint32_t tmem_base = s_tmem_base;
   volatile int *abort_flag = &s_abort;
 
-  if (warp == 0 || warp == 3) {
+  if (warp == 0 || (warp == 3 && C::kProducers == 2)) {
     // ------------------------------- TMA producers (both CTAs) -------------------------------
-    // Two threads per CTA: producer j (warp 0: j = 0, warp 3: j = 1) loads the stages whose running number
-    // is congruent to j modulo 2. A stage is one filter column and p.kbs channel blocks, one TMA instruction.
+    // With two threads per CTA (TF32 mode), producer j (warp 0: j = 0, warp 3: j = 1) loads the stages whose running
+    // number is congruent to j modulo 2. A stage is one filter column and p.kbs channel blocks, one TMA instruction.
     if (lane == 0) {
       const int j = warp == 0 ? 0 : 1;
       if (j == 0) {
@@ -192,7 +209,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const int y0 = ty * TH - p.pad_h, x0 = (rem - ty * p.tiles_w) * TW - p.pad_w;
         int kw = 0, grp = 0;
         for (int st = 0; st < p.stages_per_tile; ++st, ++g) {
-          if ((g & 1) == j) {
+          if (C::kProducers == 1 || (g & 1) == j) {
             const int s = (int)(g % kStages);
             const uint32_t ph = (uint32_t)((g / kStages) & 1);
             if (!(ok = mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, p.status, 1u))) break;
@@ -213,33 +230,40 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 || warp == 2 || warp >= C::kExtraIssuerWarp0) {
+  } else if (warp <= 3 || warp >= C::kExtraIssuerWarp0) {
     // ------------------------------- MMA issuers (even CTA) -------------------------------
-    // Issuer i runs its k-steps of every k-block into its own accumulators (buffers 2i, 2i+1).
+    // Issuer i runs its k-steps of every k-block into its own accumulators (buffers kBufs * i ...).
     if (lane == 0 && rank == 0) {
-      const int i = warp <= 2 ? warp - 1 : 2 + (warp - C::kExtraIssuerWarp0);
+      const int i = warp <= 3 ? warp - 1 : C::kLowIssuers + (warp - C::kExtraIssuerWarp0);
       constexpr int kSteps = C::kStepsPerIssuer;
       const uint32_t idesc = make_idesc_pair(p.bn, false);
       constexpr uint32_t kStep = (UMMA_K * 4) >> 4;  // 32 bytes inside the swizzle row
-      const uint64_t a_desc0 = make_smem_desc(stage_base, 16, 1024, kLayoutSw128) + (uint32_t)(kSteps * i) * kStep;
-      const uint64_t b_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128) + (uint32_t)(kSteps * i) * kStep;
+      const uint32_t step0 = SPLIT3 ? 0u : (uint32_t)i * kStep;  // TF32: this issuer's k-step of every k-block
+      const uint64_t a_desc0 = make_smem_desc(stage_base, 16, 1024, kLayoutSw128) + step0;
+      const uint64_t b_desc0 = make_smem_desc(smem_base, 16, 1024, kLayoutSw128) + step0;
       const uint32_t b_kb16 = (uint32_t)p.b_kb_bytes >> 4;
       const uint32_t b_lo16 = (uint32_t)(p.bn / 2 * 128) >> 4;
       const uint32_t stage16 = (uint32_t)stage_bytes >> 4;
       bool ok = mbar_wait(bar_bfull, 0, abort_flag, p.status, 64u);
       tc_fence_after();
-      int s = 0, slot = 0, buf = 0;
-      uint32_t ph = 0, slot_ph = 0, buf_ph = 0;
+      int s = 0, buf = 0;
+      uint32_t ph = 0, buf_ph = 0;
+      int64_t nrun = 0;  // 3xTF32: running k-block number of this pair (slot nrun % 4, owned by issuer nrun % 4)
       const uint32_t slab16 = (uint32_t)p.slab_bytes >> 4;
+      const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)i * 64;  // 3xTF32: this issuer's slot (hi, then lo)
       for (int64_t tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
         // K order of a tile: filter column kw, channel-block group, channel block q, filter row kh -- the order
-        // in which the slabs arrive. `n` counts the tile's k-blocks; 3xTF32 starts a new accumulator every
-        // kChunkKb of them.
+        // in which the slabs arrive. `n` counts the tile's k-blocks; 3xTF32 hands its accumulator to the epilogue
+        // warps every p.chunk_kb of them (if it received anything in the chunk).
         int n = 0, kw = 0, grp = 0;
-        int a = 2 * i + buf;
+        int a = C::kBufs * i + buf;
         uint32_t d_tmem = tmem_base + (uint32_t)(a * kAccCols);
-        if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
-        tc_fence_after();
+        bool active = !SPLIT3 || chunk_has(i, nrun, nrun + (p.chunk_kb < p.num_kb ? p.chunk_kb : p.num_kb));
+        uint32_t fresh = 1;  // 3xTF32: the accumulator has not received a product of this chunk yet
+        if (active) {
+          if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
+          tc_fence_after();
+        }
         for (int st = 0; st < p.stages_per_tile && ok; ++st) {
           const int nkb = p.cblocks - grp * 2 < p.kbs ? p.cblocks - grp * 2 : p.kbs;  // valid channel blocks here
           if (!SPLIT3) {
@@ -251,27 +275,33 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               const int kb = (kh * p.KW + kw) * p.cblocks + grp * 2 + q;  // this k-block's slice of the filter
               const uint64_t b_d = b_desc0 + (uint32_t)kb * b_kb16;
               if (SPLIT3) {
-                if (n && n % kChunkKb == 0) {
-                  // chunk boundary: publish this accumulator, continue in the other one
-                  umma_commit_pair_both(bar_tfull + 8 * a, 3);
-                  if (++buf == 2) { buf = 0; buf_ph ^= 1; }
-                  a = 2 * i + buf;
-                  d_tmem = tmem_base + (uint32_t)(a * kAccCols);
-                  if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
+                if (n && n % p.chunk_kb == 0) {
+                  // chunk boundary: publish the accumulator, take it back once the epilogue warps have read it
+                  if (active) {
+                    umma_commit_pair_both(bar_tfull + 8 * a, 3);
+                    buf_ph ^= 1;
+                  }
+                  const int64_t c0 = nrun, left = p.num_kb - n;
+                  active = chunk_has(i, c0, c0 + (p.chunk_kb < left ? p.chunk_kb : left));
+                  fresh = 1;
+                  if (active) {
+                    if (!(ok = mbar_wait(bar_tempty + 8 * a, buf_ph ^ 1, abort_flag, p.status, 2u))) break;
+                    tc_fence_after();
+                  }
+                }
+                if ((int)(nrun & 3) == i) {
+                  if (!(ok = mbar_wait(bar_split + 8 * i, (uint32_t)(nrun >> 2) & 1u, abort_flag, p.status, 4u))) break;
                   tc_fence_after();
-                }
-                const uint32_t first = n % kChunkKb ? 1u : 0u;
-                if (!(ok = mbar_wait(bar_split + 8 * slot, slot_ph, abort_flag, p.status, 4u))) break;
-                tc_fence_after();
-                const uint32_t a_t = tmem_base + C::kSlotCol0 + (uint32_t)slot * 64 + (uint32_t)(kSteps * i) * UMMA_K;
 #pragma unroll
-                for (int j = 0; j < kSteps; ++j) {
-                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K + 32, b_d + j * kStep, idesc, j > 0 ? 1u : first);  // lo * hi
-                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + b_lo16 + j * kStep, idesc, 1u);              // hi * lo
-                  umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + j * kStep, idesc, 1u);                       // hi * hi
+                  for (int j = 0; j < kSteps; ++j) {
+                    umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K + 32, b_d + j * kStep, idesc, j > 0 ? 1u : fresh ^ 1u);  // lo * hi
+                    umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + b_lo16 + j * kStep, idesc, 1u);                   // hi * lo
+                    umma_tf32_ts_pair(d_tmem, a_t + j * UMMA_K, b_d + j * kStep, idesc, 1u);                            // hi * hi
+                  }
+                  fresh = 0;
+                  umma_commit_pair_both(bar_slotfree + 8 * i, 3);
                 }
-                umma_commit_pair_both(bar_slotfree + 8 * slot, 3);
-                if (++slot == kSlots) { slot = 0; slot_ph ^= 1; }
+                ++nrun;
               } else {
                 // rows [8 kh, 8 kh + 128) of channel block q of the slab: kh image rows = kh * 1024 bytes down
                 const uint64_t a_d = a_desc0 + (uint32_t)s * stage16 + (uint32_t)q * slab16 + (uint32_t)kh * (1024 >> 4);
@@ -289,8 +319,10 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           if (++grp == p.groups) { grp = 0; ++kw; }
         }
         if (!ok) break;
-        umma_commit_pair_both(bar_tfull + 8 * a, 3);
-        if (++buf == 2) { buf = 0; buf_ph ^= 1; }
+        if (active) {
+          umma_commit_pair_both(bar_tfull + 8 * a, 3);
+          if (++buf == C::kBufs) { buf = 0; buf_ph ^= 1; }
+        }
       }
     }
   } else if (warp >= C::kEpilogueWarp0 && warp < C::kSplitWarp0) {
@@ -302,31 +334,44 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tempty0 = rank == 0 ? bar_tempty : map_to_cta(bar_tempty, 0);
     const int64_t plane = (int64_t)p.OH * p.OW;
     int buf = 0;
-    uint32_t buf_ph = 0;
+    uint32_t buf_ph = 0;  // TF32: phase of the accumulator pair in use; 3xTF32: bit i = phase of accumulator i
+    int64_t nrun = 0;     // 3xTF32: running k-block number of this pair at the start of the tile
     bool ok = true;
-    const int chunk = SPLIT3 ? kChunkKb : p.num_kb;
+    const int chunk = SPLIT3 ? p.chunk_kb : p.num_kb;
     for (int64_t tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
       float sum[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) sum[j] = 0.f;
       for (int kb0 = 0; kb0 < p.num_kb; kb0 += chunk) {
+        // 3xTF32: an accumulator takes part in the chunk if its issuer owned a k-block of it
+        const int kb1 = kb0 + chunk < p.num_kb ? kb0 + chunk : p.num_kb;
+        bool act[C::kIssuers];
 #pragma unroll
-        for (int i = 0; i < C::kIssuers; ++i)
-          if (ok) ok = mbar_wait(bar_tfull + 8 * (2 * i + buf), buf_ph, abort_flag, p.status, 8u);
+        for (int i = 0; i < C::kIssuers; ++i) {
+          act[i] = !SPLIT3 || chunk_has(i, nrun + kb0, nrun + kb1);
+          const uint32_t ph = SPLIT3 ? (buf_ph >> i) & 1u : buf_ph;
+          if (ok && act[i]) ok = mbar_wait(bar_tfull + 8 * (C::kBufs * i + buf), ph, abort_flag, p.status, 8u);
+        }
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 32; c += 16) {
-          uint32_t v[C::kIssuers][16];
+          // accumulators are read kLdGroup at a time (register budget: 672 threads in 3xTF32 mode)
+          constexpr int kLdGroup = SPLIT3 ? 2 : C::kIssuers;
 #pragma unroll
-          for (int i = 0; i < C::kIssuers; ++i) tmem_ld16(lane_addr + (uint32_t)((2 * i + buf) * kAccCols + c), v[i]);
-          tmem_ld_wait();
+          for (int i0 = 0; i0 < C::kIssuers; i0 += kLdGroup) {
+            uint32_t v[kLdGroup][16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float t = __uint_as_float(v[0][j]);
+            for (int i = 0; i < kLdGroup; ++i)
+              tmem_ld16(lane_addr + (uint32_t)((C::kBufs * (i0 + i) + buf) * kAccCols + c), v[i]);
+            tmem_ld_wait();
 #pragma unroll
-            for (int i = 1; i < C::kIssuers; ++i) t += __uint_as_float(v[i][j]);
-            sum[c + j] += t;
+            for (int j = 0; j < 16; ++j) {
+              float t = 0.f;
+#pragma unroll
+              for (int i = 0; i < kLdGroup; ++i) t += act[i0 + i] ? __uint_as_float(v[i][j]) : 0.f;
+              sum[c + j] += t;
+            }
           }
         }
         tc_fence_before();
@@ -334,12 +379,21 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (lane == 0) {
 #pragma unroll
           for (int i = 0; i < C::kIssuers; ++i) {
-            if (rank == 0) mbar_arrive(bar_tempty + 8 * (2 * i + buf));
-            else mbar_arrive_cluster_relaxed(tempty0 + 8 * (2 * i + buf));
+            if (!act[i]) continue;
+            if (rank == 0) mbar_arrive(bar_tempty + 8 * (C::kBufs * i + buf));
+            else mbar_arrive_cluster_relaxed(tempty0 + 8 * (C::kBufs * i + buf));
           }
         }
-        if (++buf == 2) { buf = 0; buf_ph ^= 1; }
+        if (SPLIT3) {
+#pragma unroll
+          for (int i = 0; i < C::kIssuers; ++i)
+            if (act[i]) buf_ph ^= 1u << i;
+        } else if (++buf == C::kBufs) {
+          buf = 0;
+          buf_ph ^= 1;
+        }
       }
+      nrun += p.num_kb;
       if (!ok) break;
       // this thread's output pixel: row r of the tile is pixel (r / 8, r % 8)
       const int64_t ct = 2 * tile + (int64_t)rank;
@@ -414,11 +468,13 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
                 const float4 x = arow[(half * 4 + c) ^ (srow & 7)];
-                const float h0 = to_tf32_rna(x.x), h1 = to_tf32_rna(x.y), h2 = to_tf32_rna(x.z), h3 = to_tf32_rna(x.w);
-                hi[4 * c + 0] = __float_as_uint(h0); hi[4 * c + 1] = __float_as_uint(h1);
-                hi[4 * c + 2] = __float_as_uint(h2); hi[4 * c + 3] = __float_as_uint(h3);
-                lo[4 * c + 0] = __float_as_uint(to_tf32_rna(x.x - h0)); lo[4 * c + 1] = __float_as_uint(to_tf32_rna(x.y - h1));
-                lo[4 * c + 2] = __float_as_uint(to_tf32_rna(x.z - h2)); lo[4 * c + 3] = __float_as_uint(to_tf32_rna(x.w - h3));
+                const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const uint32_t h = split_hi(xs[e]);
+                  hi[4 * c + e] = h;
+                  lo[4 * c + e] = split_hi(xs[e] - __uint_as_float(h));
+                }
               }
               if (half == 0) {
                 // the slot was last read by the MMAs of the k-block kSlots before this one
@@ -672,6 +728,10 @@ int conv2d_run(cudaStream_t st, const b200_conv_desc &d, int flags, const float 
   p.tiles_per_img = p.tiles_w * (int)((OH + TH - 1) / TH);
   p.cblocks = Cp / 32;
   p.num_kb = pl.num_kb;
+  {
+    const int nchunks = (pl.num_kb + kMaxChunkKb - 1) / kMaxChunkKb;
+    p.chunk_kb = (pl.num_kb + nchunks - 1) / nchunks;
+  }
   p.kbs = pl.kbs;
   p.groups = pl.groups;
   p.stages_per_tile = (int)d.KW * pl.groups;
