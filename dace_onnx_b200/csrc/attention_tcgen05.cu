@@ -77,10 +77,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t bar0 = smem_u32(bars);
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_exp_turn[4];  // per scheduler: which slot's softmax warp is in its exponential pass (0 = none)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
+    for (int i = 0; i < 4; ++i) s_exp_turn[i] = 0;
     for (int s = 0; s < 2; ++s)
       for (int i = 0; i < kSlotBars; ++i)
         mbar_init(bar0 + 8 * (s * kSlotBars + i), (i == kPFull0 || i == kPFull1) ? 4 : (i == kPvDone ? 2 : 1));
@@ -258,6 +260,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
         }
         // ---- P = exp2(s * c - off) in place, 64 columns (one P V issuer's share) at a time ----
+        // The two slots' warps of one scheduler share its special-function unit; taking turns keeps the slots in
+        // anti-phase (one in its exponentials while the other's MMAs run) instead of both at half speed.
+        if (lane == 0) {
+          const long long t_lock = clock64();
+          while (atomicCAS(&s_exp_turn[quarter], 0, 1) != 0) {
+            if (*abort_flag) break;
+            if (clock64() - t_lock > kWaitCycleBudget) {
+              *abort_flag = 1;
+              atomicOr(p.status, 8u);
+              break;
+            }
+          }
+        }
+        __syncwarp();
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
         for (int hb = 0; hb < 2; ++hb) {
@@ -287,6 +303,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(bar + 8 * (hb ? kPFull1 : kPFull0));
         }
+        if (lane == 0) atomicExch(&s_exp_turn[quarter], 0);
         l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
         m_run = m_new;
       }
