@@ -79,7 +79,14 @@ class ClockSampler:
             if len(parts) >= 9:
                 self.samples.append(parts)
 
-    def stop(self):
+    def mark(self):
+        """Number of samples taken so far (call at the start of the timed region)."""
+        return len(self.samples)
+
+    def stop(self, first=0):
+        """Summary of the samples taken since `first` (see mark()). A timed region shorter than the sampling period
+        may hold none: the last warm-up samples (the same load, immediately before) then stand in, and the record
+        says so."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -87,15 +94,20 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        mhz = sorted(int(float(s[1])) for s in self.samples if s[1].replace(".", "").isdigit())
-        mx = [int(float(s[2])) for s in self.samples if s[2].replace(".", "").isdigit()]
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        taken, source = self.samples[first:], "timed region"
+        if not taken and self.samples:
+            taken, source = self.samples[max(0, first - 3):first] or self.samples[-3:], "warm-up steps just before the timed region"
+        mhz = sorted(int(float(s[1])) for s in taken if s[1].replace(".", "").isdigit())
+        mx = [int(float(s[2])) for s in taken if s[2].replace(".", "").isdigit()]
         reasons = set()
-        for s in self.samples:
+        for s in taken:
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(self.samples)}
+                "reasons": sorted(reasons), "samples": len(taken), "sampled_during": source}
 
 
 def cpu_baseline_sample(layers, hidden, heads, ffn, seq, sample_seqs, reps, warmup):
@@ -216,10 +228,12 @@ def run_b200(args, wl):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()  # before the warm-up: nvidia-smi needs a few hundred ms before its first sample
     for _ in range(args.warmup):
         step_device()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    torch.cuda.synchronize()
+    first_sample = sampler.mark()
     enc.timeline = []
     del gather_events[:]
     launches0 = enc.launches
@@ -227,7 +241,7 @@ def run_b200(args, wl):
     launches = enc.launches - launches0
     timeline, enc.timeline = enc.timeline, None
     gathers = list(gather_events)
-    clocks = sampler.stop()
+    clocks = sampler.stop(first_sample)
     for _ in range(min(args.warmup, 1)):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)

@@ -56,6 +56,27 @@ def test_fused_attention_sharp_rows_and_separate_tensors(cuda):
     close(out.permute(0, 2, 1, 3), un, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("S", [384, 512, 160])
+def test_running_maximum_moves_between_key_blocks(S, cuda):
+    # Scores that grow by 64 per block of 128 keys for the even query rows (the kernel's exponent offset must follow:
+    # 64 * 0.125 * log2(e) > 8, so the partial outputs accumulated so far are rescaled at every block) and fall by
+    # 64 per block for the odd rows (offset fixed by the first block) - both kinds in every warp. All scores are
+    # small integers, exact in TF32, so the comparison with the fp32 oracle stays at the TF32 tolerance of P and V.
+    B, H, D = 2, 2, 64
+    g = torch.Generator().manual_seed(S)
+    q = torch.zeros(B, S, H, D)
+    q[:, 0::2, :, 0] = 1.0
+    q[:, 1::2, :, 0] = -1.0
+    t = torch.arange(S)
+    k = torch.randn(B, S, H, D, generator=g)
+    k[:, :, :, 0] = (64 * (t // 128) + (t % 7)).float()[None, :, None]
+    v = torch.randn(B, S, H, D, generator=g)
+    out = torch.empty(B, S, H, D, device="cuda")
+    assert ops.attention_views(q.cuda(), k.cuda(), v.cuda(), out, 0.125, math_mode="tf32")
+    ref = oracle_attention(q, k, v, 0.125)
+    close(out, ref, TF32_RTOL, TF32_ATOL)
+
+
 def test_rows_are_convex_combinations_at_bench_size(cuda):
     # V = 1 everywhere -> every output element is sum(P)/sum(P) = 1 up to the TF32 cut of P
     B, S, H, D = 128, 384, 16, 64
