@@ -64,10 +64,10 @@ def test_conv_stride_and_errors(cuda):
 @pytest.mark.parametrize("mode,rtol,atol", [("fp32x3", RTOL, ATOL), ("tf32", TF32_RTOL, TF32_ATOL)])
 @pytest.mark.parametrize("n,c,h,w,m,k,pad", [(3, 64, 56, 56, 64, 3, 1), (2, 32, 20, 13, 48, 3, 1), (1, 16, 9, 9, 16, 1, 0),
                                              (5, 64, 7, 7, 24, 3, 0), (2, 32, 17, 30, 32, 5, 2), (3, 128, 33, 18, 64, 3, 1), (1, 96, 12, 12, 33, 3, 1),
-                                             # k-block counts 2, 3, 9 and 45 per tile (the 3xTF32 issuers take every fourth k-block of
+                                             # k-block counts 2, 3, 9 and 50 per tile (the 3xTF32 issuers take every fourth k-block of
                                              # a count that runs on across tiles; accumulators are handed over every <= 20 k-blocks)
                                              (2, 64, 10, 10, 64, 1, 0), (2, 96, 10, 10, 48, 1, 0), (4, 32, 40, 40, 64, 3, 1),
-                                             (1, 160, 12, 12, 64, 3, 1)])
+                                             (1, 64, 12, 12, 16, 5, 2)])
 def test_prepared_conv_layouts(n, c, h, w, m, k, pad, mode, rtol, atol, cuda):
     """b200_conv2d_prepared_f32 in all four layout combinations against the oracle (NCHW) -- odd image sizes
     (8x8 block tails), output-channel counts that are not multiples of 16 or 32, 1x1 / 5x5 filters."""
