@@ -38,22 +38,81 @@ __device__ __forceinline__ float4 apply_binary4(float4 a, float4 b) {
 // rows x cols view; each operand advances by (rs, cs) elements per (row, column) with cs in {0,1}.
 // One float4 of output per thread per iteration; requires cols % 4 == 0 and 16-byte alignment of
 // every operand that is read as a vector.
-template <int OP>
+template <int OP, int RU>
 __global__ void __launch_bounds__(256)
 binary_rc_vec_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c,
                      int64_t rows, int64_t cols4, int64_t a_rs, int a_cs, int64_t b_rs, int b_cs) {
-  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
-    const float *ar = a + r * a_rs;
-    const float *br = b + r * b_rs;
-    float *cr = c + r * cols4 * 4;
-    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < cols4;
-         j += (int64_t)gridDim.x * blockDim.x) {
-      float4 va, vb;
-      if (a_cs) va = ld_stream4(ar + 4 * j);
-      else { float t = __ldg(ar); va = make_float4(t, t, t, t); }
-      if (b_cs) vb = ld_stream4(br + 4 * j);
-      else { float t = __ldg(br); vb = make_float4(t, t, t, t); }
-      st_stream4(cr + 4 * j, apply_binary4<OP>(va, vb));
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  if (RU == 1) {
+    if (rows == 1 && gridDim.y == 1) {
+      // one long row (flattened tensors): every block walks chunks of 4 x 256 consecutive vectors, four
+      // independent groups of loads in flight per thread, all in the same 16 KiB
+      const int64_t chunks = cols4 / (4 * 256);
+      for (int64_t ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
+        const int64_t base = ch * (4 * 256) + threadIdx.x;
+        float4 va[4], vb[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t j = base + u * 256;
+          if (a_cs) va[u] = ld_stream4(a + 4 * j);
+          else { float t = __ldg(a); va[u] = make_float4(t, t, t, t); }
+          if (b_cs) vb[u] = ld_stream4(b + 4 * j);
+          else { float t = __ldg(b); vb[u] = make_float4(t, t, t, t); }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) st_stream4(c + 4 * (base + u * 256), apply_binary4<OP>(va[u], vb[u]));
+      }
+      for (int64_t j = chunks * (4 * 256) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < cols4; j += step) {
+        float4 va, vb;
+        if (a_cs) va = ld_stream4(a + 4 * j);
+        else { float t = __ldg(a); va = make_float4(t, t, t, t); }
+        if (b_cs) vb = ld_stream4(b + 4 * j);
+        else { float t = __ldg(b); vb = make_float4(t, t, t, t); }
+        st_stream4(c + 4 * j, apply_binary4<OP>(va, vb));
+      }
+      return;
+    }
+    // few (long) rows: one column group per thread and iteration
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+      const float *ar = a + r * a_rs;
+      const float *br = b + r * b_rs;
+      float *cr = c + r * cols4 * 4;
+      for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < cols4; j += step) {
+        float4 va, vb;
+        if (a_cs) va = ld_stream4(ar + 4 * j);
+        else { float t = __ldg(ar); va = make_float4(t, t, t, t); }
+        if (b_cs) vb = ld_stream4(br + 4 * j);
+        else { float t = __ldg(br); vb = make_float4(t, t, t, t); }
+        st_stream4(cr + 4 * j, apply_binary4<OP>(va, vb));
+      }
+    }
+    return;
+  }
+  // Many rows (activations [tokens, hidden] with a bias or scale row, or a per-row scalar): columns outside, rows
+  // inside, RU rows per iteration, i.e. up to 2 RU independent 16-byte loads in flight per thread. An operand that
+  // is the same for every row (row stride 0) stays in L1; everything else streams past it.
+  const int64_t rstep = gridDim.y;
+  const bool a_keep = a_rs == 0, b_keep = b_rs == 0;
+  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < cols4; j += step) {
+    for (int64_t r0 = blockIdx.y; r0 < rows; r0 += RU * rstep) {
+      float4 va[RU], vb[RU];
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int64_t r = r0 + u * rstep;
+        if (r < rows) {
+          const float *ar = a + r * a_rs;
+          const float *br = b + r * b_rs;
+          if (a_cs) va[u] = a_keep ? __ldg(reinterpret_cast<const float4 *>(ar + 4 * j)) : ld_stream4(ar + 4 * j);
+          else { float t = __ldg(ar); va[u] = make_float4(t, t, t, t); }
+          if (b_cs) vb[u] = b_keep ? __ldg(reinterpret_cast<const float4 *>(br + 4 * j)) : ld_stream4(br + 4 * j);
+          else { float t = __ldg(br); vb[u] = make_float4(t, t, t, t); }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < RU; ++u) {
+        const int64_t r = r0 + u * rstep;
+        if (r < rows) st_stream4(c + (r * cols4 + j) * 4, apply_binary4<OP>(va[u], vb[u]));
+      }
     }
   }
 }
@@ -91,7 +150,22 @@ unary_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t numel, 
   const int64_t nth = (int64_t)gridDim.x * blockDim.x;
   if (vec) {
     const int64_t n4 = numel >> 2;
-    for (int64_t i = tid; i < n4; i += nth) {
+    // Each block walks chunks of 4 x 256 consecutive vectors: four independent 16-byte loads in flight per thread,
+    // all in the same 16 KiB of memory.
+    const int64_t chunks = n4 / (4 * 256);
+    for (int64_t ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
+      const int64_t base = ch * (4 * 256) + threadIdx.x;
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = ld_stream4(x + 4 * (base + u * 256));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u].x = apply_unary<OP>(v[u].x); v[u].y = apply_unary<OP>(v[u].y);
+        v[u].z = apply_unary<OP>(v[u].z); v[u].w = apply_unary<OP>(v[u].w);
+        st_stream4(y + 4 * (base + u * 256), v[u]);
+      }
+    }
+    for (int64_t i = chunks * (4 * 256) + tid; i < n4; i += nth) {
       float4 v = ld_stream4(x + 4 * i);
       v.x = apply_unary<OP>(v.x); v.y = apply_unary<OP>(v.y);
       v.z = apply_unary<OP>(v.z); v.w = apply_unary<OP>(v.w);
@@ -236,8 +310,12 @@ int launch_binary(cudaStream_t st, const float *a, const float *b, float *c, int
     const int64_t want = ((int64_t)kNumSMs * 16 + gx - 1) / gx;
     if (gy > want) gy = want;
     if (gy > 65535) gy = 65535;
-    binary_rc_vec_kernel<OP><<<dim3(gx, (unsigned)gy), 256, 0, st>>>(a, b, c, rows, cols4, a_rs, (int)a_cs, b_rs,
-                                                                    (int)b_cs);
+    if (rows >= 4 * gy)
+      binary_rc_vec_kernel<OP, 4><<<dim3(gx, (unsigned)gy), 256, 0, st>>>(a, b, c, rows, cols4, a_rs, (int)a_cs, b_rs,
+                                                                         (int)b_cs);
+    else
+      binary_rc_vec_kernel<OP, 1><<<dim3(gx, (unsigned)gy), 256, 0, st>>>(a, b, c, rows, cols4, a_rs, (int)a_cs, b_rs,
+                                                                         (int)b_cs);
     return check_launch("binary_rc_vec");
   }
   StridedArgs args;
