@@ -296,7 +296,9 @@ def run_node(dace, op, out_shape, inputs, **attrs):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_reference_pins.py <checkout of spcl/dace-onnx (daceml)>")
+    root = sys.argv[1]
     dace = install_fakes()
     load_reference(root)
     r = np.random.default_rng(2024)
