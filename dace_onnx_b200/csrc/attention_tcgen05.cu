@@ -35,17 +35,21 @@ constexpr int kBlkBytes = 128 * kD * 4; // 32 KiB: 128 rows x 64 fp32 as two sli
 //   warps 2-3    score issuer of slot 0 / 1:  S = Q K_j^T                          (kind::tf32, A and B in smem)
 //   warps 4-7    P V issuers, two per slot: first / second 64 keys of the block into partial output 0 / 1
 //                (A = P from TMEM); each starts as soon as its 64 columns of P are published
-//   warps 8-15   softmax and output, four per slot: one score row per thread
+//   warps 8-15   softmax, four per slot: one score row per thread
+//   warps 16-19  output, both slots in turn: add the two partial outputs, divide by the row sum, store (kept off the
+//                softmax warps, whose next tile would otherwise wait ~3K clk for the last P V and the stores)
 // so that one slot's MMAs run while the other slot's softmax warps are busy. Keys are walked in blocks of 128
 // with a running maximum; the exponent offset follows it only when it has grown by more than 2^8, so the
 // outputs accumulate in TMEM across blocks and are rescaled rarely. Any sequence length that is a multiple of 32.
 // Barriers of a slot (all single-buffered, phase = block or tile count modulo 2):
 //   q_full / q_empty, k_full / k_empty, v_full      loads (a value block is free again at pv_done)
 //   s_full    score issuer -> softmax          p_full[2]   softmax (one arrival per warp) -> P V issuer 0 / 1
-//   pv_done   both P V issuers -> score issuer (score columns free), producer, softmax (output complete)
+//   pv_done   both P V issuers -> score issuer (score columns free), producer, softmax, output warps
+//   l_ready   softmax (row sums of the finished tile in shared memory) -> output warps
+//   o_free    output warps (partial outputs read) -> P V issuers (the next tile may overwrite them)
 // ---------------------------------------------------------------------------------------------
-constexpr int kThreads = 32 * 16;
-enum SlotBar { kQFull = 0, kQEmpty, kKFull, kKEmpty, kVFull, kSFull, kPFull0, kPFull1, kPvDone, kSlotBars };
+constexpr int kThreads = 32 * 20;
+enum SlotBar { kQFull = 0, kQEmpty, kKFull, kKEmpty, kVFull, kSFull, kPFull0, kPFull1, kPvDone, kLReady, kOFree, kSlotBars };
 
 struct AttnParams {
   int S, heads, n_blocks;
@@ -77,6 +81,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t bar0 = smem_u32(bars);
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_rowsum[2][128];  // [slot][row]: row sums of the tile the output warps are about to finish
   __shared__ int s_exp_turn[4];  // per scheduler: which slot's softmax warp is in its exponential pass (0 = none)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -85,7 +90,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int i = 0; i < 4; ++i) s_exp_turn[i] = 0;
     for (int s = 0; s < 2; ++s)
       for (int i = 0; i < kSlotBars; ++i)
-        mbar_init(bar0 + 8 * (s * kSlotBars + i), (i == kPFull0 || i == kPFull1) ? 4 : (i == kPvDone ? 2 : 1));
+        mbar_init(bar0 + 8 * (s * kSlotBars + i),
+                  (i == kPFull0 || i == kPFull1 || i == kLReady || i == kOFree) ? 4 : (i == kPvDone ? 2 : 1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -99,7 +105,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   volatile int *abort_flag = &s_abort;
   const int nb = p.n_blocks;
   // role and slot of this warp
-  const int slot = warp < 2 ? warp : (warp < 4 ? warp - 2 : (warp < 8 ? (warp - 4) >> 1 : (warp - 8) >> 2));
+  const int slot = warp < 2 ? warp : (warp < 4 ? warp - 2 : (warp < 8 ? (warp - 4) >> 1 : (warp < 16 ? (warp - 8) >> 2 : 0)));
   const uint32_t bar = bar0 + 8 * (slot * kSlotBars);
   const uint32_t q_smem = smem0 + slot * kBlkBytes, k_smem = smem0 + (2 + slot) * kBlkBytes,
                  v_smem = smem0 + (4 + slot) * kBlkBytes;
@@ -168,13 +174,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const uint32_t idesc_o = make_idesc(kD, true);
       const uint64_t v_base = make_smem_desc(0, kBlkBytes / 2, 512, kLayoutSw128Base32) + (v_smem >> 4);
       const uint32_t p_bar = bar + 8 * (second ? kPFull1 : kPFull0);
-      int64_t g = 0;
-      for (int64_t t = t0; t < p.tiles && ok; t += t_step) {
+      int64_t g = 0, n = 0;
+      for (int64_t t = t0; t < p.tiles && ok; t += t_step, ++n) {
         uint32_t started = 0;  // 0 until this accumulator has received its first product of the tile
         for (int j = 0; j < nb; ++j, ++g) {
           const uint32_t ph = (uint32_t)(g & 1);
           if (!(ok = mbar_wait(bar + 8 * kVFull, ph, abort_flag, p.status, 4u))) break;
           if (!(ok = mbar_wait(p_bar, ph, abort_flag, p.status, 4u))) break;
+          // the previous tile's partial outputs must have been read before the first product overwrites them
+          if (j == 0 && !(ok = mbar_wait(bar + 8 * kOFree, (uint32_t)(n & 1) ^ 1, abort_flag, p.status, 4u))) break;
           tc_fence_after();
           const int k_len = p.S - j * 128 < 128 ? p.S - j * 128 : 128;
           // 8 key rows of V (8 x 128 B = 64 descriptor units) and 8 columns of P per MMA
@@ -196,8 +204,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
     }
-  } else {
-    // ------------------------------- softmax + output of the slot -------------------------------
+  } else if (warp < 16) {
+    // ------------------------------- softmax of the slot -------------------------------
     // One score row per thread (warp w of the slot's four reads TMEM lanes 32 w ...): no exchange between threads.
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
@@ -308,39 +316,66 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         m_run = m_new;
       }
       if (!ok) break;
-      // ---- normalise and store once the last block's P V has been accumulated ----
-      if (!(ok = mbar_wait(bar + 8 * kPvDone, (uint32_t)((g - 1) & 1), abort_flag, p.status, 8u))) break;
-      tc_fence_after();
-      const int64_t item = t / nb;
-      const int mt = (int)(t - item * nb), b = (int)(item / p.heads), h = (int)(item % p.heads);
-      const int row = mt * 128 + row_in_tile;
-      const float inv = 1.0f / l_run;
-      float *orow = p.out + (int64_t)b * p.o_batch + (int64_t)row * p.o_row + (int64_t)h * p.o_head;
+      // hand the tile's row sums to the output warps (they waited for o_free's predecessor, so the previous tile's
+      // sums have been read) and go on with the next tile
+      s_rowsum[slot][row_in_tile] = l_run;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar + 8 * kLReady);
+    }
+  } else {
+    // ------------------------------- output, both slots in turn -------------------------------
+    // Tile i of slot 0, tile i of slot 1, tile i + 1 of slot 0, ...: once the tile's last P V is complete, add the
+    // two partial outputs, release them (o_free), divide by the row sum and store [row, head * 64 ... + 64).
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    for (int64_t i = 0; ok; ++i) {
+      const int64_t ta = 2 * (int64_t)blockIdx.x + i * t_step;
+      if (ta >= p.tiles) break;  // slot 0 has no tile i: slot 1 has none either
 #pragma unroll 1
-      for (int c0 = 0; c0 < kD; c0 += 32) {
-        uint32_t o[32];
-        tmem_ld32(o0_tmem + lane_off + c0, o);
-        if (p.S > 64) {  // the second partial output exists once a block has more than 64 keys
-          uint32_t o2[32];
-          tmem_ld32(o1_tmem + lane_off + c0, o2);
+      for (int sl = 0; sl < 2 && ok; ++sl) {
+        const int64_t t = ta + sl;
+        if (t >= p.tiles) break;
+        const uint32_t sbar = bar0 + 8 * (sl * kSlotBars);
+        const uint32_t o_tmem = tmem_base + sl * 256 + 128 + lane_off;  // partial outputs: columns [128, 192), [192, 256)
+        if (!(ok = mbar_wait(sbar + 8 * kLReady, (uint32_t)(i & 1), abort_flag, p.status, 16u))) break;
+        if (!(ok = mbar_wait(sbar + 8 * kPvDone, (uint32_t)(((i + 1) * nb - 1) & 1), abort_flag, p.status, 16u))) break;
+        tc_fence_after();
+        const float inv = 1.0f / s_rowsum[sl][row_in_tile];
+        const int64_t item = t / nb;
+        const int mt = (int)(t - item * nb), b = (int)(item / p.heads), h = (int)(item % p.heads);
+        const int row = mt * 128 + row_in_tile;
+        float *orow = p.out + (int64_t)b * p.o_batch + (int64_t)row * p.o_row + (int64_t)h * p.o_head;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kD; c0 += 32) {  // 32 output columns at a time (register budget)
+          uint32_t o[32];
+          tmem_ld32(o_tmem + c0, o);
+          if (p.S > 64) {  // the second partial output exists once a block has more than 64 keys
+            uint32_t o2[32];
+            tmem_ld32(o_tmem + 64 + c0, o2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) + __uint_as_float(o2[k]));
+          }
           tmem_ld_wait();
+          if (c0 + 32 >= kD) {  // everything read: the next tile's P V may overwrite the partial outputs
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sbar + 8 * kOFree);
+          }
+          if (row < p.S) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) + __uint_as_float(o2[i]));
-        }
-        tmem_ld_wait();
-        if (row < p.S) {
+            for (int k = 0; k < 32; k += 8) {
+              float r[8];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            float r[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) r[q] = __uint_as_float(o[i + q]) * inv;
-            asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow + c0 + i), "f"(r[0]), "f"(r[1]),
-                         "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7])
-                         : "memory");
+              for (int q = 0; q < 8; ++q) r[q] = __uint_as_float(o[k + q]) * inv;
+              asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(orow + c0 + k), "f"(r[0]), "f"(r[1]),
+                           "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7])
+                           : "memory");
+            }
           }
         }
       }
-      tc_fence_before();
     }
   }
 
