@@ -1373,6 +1373,14 @@ static bool pair3_qualifies(const b200_gemm_desc &d) {
   const int64_t cols = d.trans_b ? d.K : d.N;
   return d.math_mode == B200_MATH_FP32X3 && d.batch_outer * d.batch_inner == 1 && d.M > BM && cols % 4 == 0;
 }
+static size_t pair3_workspace_bytes(const b200_gemm_desc &d) {
+  const int64_t rows = d.trans_b ? d.N : d.K, cols = d.trans_b ? d.K : d.N;
+  return 2 * align256((size_t)rows * (size_t)cols * 4);
+}
+// Below ~9 GFLOP the extra launch of the split kernel and the pair kernel's longer prologue cost more than its
+// faster main loop saves (measured: [4096,120] x 784 33 -> 29 us, [4096,84] x 120 19 -> 13 us on the plain path;
+// [8192,768] x 768 66 -> 56 us with the workspace): such calls are told to bring no workspace.
+static bool pair3_worth_it(const b200_gemm_desc &d) { return (double)d.M * (double)d.N * (double)d.K >= 4.5e9; }
 
 // BF16 mode: one matrix (no batch). Both operands are converted into the workspace, K padded to a multiple of 8.
 static bool bf16_qualifies(const b200_gemm_desc &d) {
@@ -1382,9 +1390,8 @@ static size_t bf16_operand_bytes(int64_t rows, int64_t K) { return align256((siz
 
 size_t gemm_tc_workspace_bytes(const b200_gemm_desc &d) {
   if (bf16_qualifies(d)) return bf16_operand_bytes(d.M, d.K) + bf16_operand_bytes(d.N, d.K);
-  if (!pair3_qualifies(d)) return 0;
-  const int64_t rows = d.trans_b ? d.N : d.K, cols = d.trans_b ? d.K : d.N;
-  return 2 * align256((size_t)rows * (size_t)cols * 4);
+  if (!pair3_qualifies(d) || !pair3_worth_it(d)) return 0;
+  return pair3_workspace_bytes(d);
 }
 
 // BF16 mode: A and B are rounded to bf16 into the workspace (B transposed to [N, K] when it is given as [K, N]), then
@@ -1462,8 +1469,9 @@ int gemm_tc(cudaStream_t st, const b200_gemm_desc &d_in, const float *A, const f
     d.math_mode = B200_MATH_TF32;  // batched operands (attention heads addressed in place) keep the TF32 kernels
   }
   const bool split3 = d.math_mode == B200_MATH_FP32X3;
+  // a caller that brings the split workspace anyway gets the pair kernel whatever the size
   const bool pair3 = workspace && aligned16(workspace) && pair3_qualifies(d) &&
-                     workspace_bytes >= gemm_tc_workspace_bytes(d);
+                     workspace_bytes >= pair3_workspace_bytes(d);
   // pair kernel: 192-column tiles unless their padding costs more than the slower 128-column instructions
   const bool pair3_wide = ((d.N + 191) / 192) * 192 <= ((d.N + 127) / 128) * 128 * 1.3;
   const int bn = pair3 ? (pair3_wide ? 192 : 128) : pick_bn(d.N, split3);

@@ -117,7 +117,9 @@ B200_API int b200_gemm_f32(void *stream, const b200_gemm_desc *desc, const float
 
 /* The same contraction with device scratch, the way the reference's library-call expansions get a workspace
  * from their SDFG init hook (cudnn_implementations.py:281-301). With b200_gemm_workspace_bytes(desc) bytes of
- * 16-byte aligned scratch (0 = this call has no use for one), the fp32-accurate mode (B200_MATH_FP32X3) splits
+ * 16-byte aligned scratch (0 = this call has no use for one: other modes, batched operands, or a product of
+ * less than ~9 GFLOP, where the split's extra launch costs more than it saves), the fp32-accurate mode
+ * (B200_MATH_FP32X3) splits
  * B once into its two TF32 halves there and runs a faster two-CTA kernel; results follow the same 3xTF32
  * arithmetic as b200_gemm_f32. A null or too small workspace is not an error in that mode: the call then behaves
  * exactly like b200_gemm_f32. B200_MATH_BF16 needs the workspace (it holds the bf16 copies of A and B) and returns
