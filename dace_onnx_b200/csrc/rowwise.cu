@@ -236,6 +236,9 @@ layernorm_warp_vec_kernel(const float *__restrict__ x, const float *__restrict__
 // flight with cp.async.bulk (a row is one contiguous block of global memory, so one instruction by one lane moves
 // it and signals an mbarrier): ~190 KiB in flight per SM regardless of what the warps are doing, where register
 // staging keeps only what the resident warps have issued. gamma / beta live in registers for the whole kernel.
+// Rows are walked from the last to the first, with plain (not evict-first) stores: a tensor this size is usually
+// the output of a GEMM whose last tiles are still in L2 when this kernel starts, and the GEMM that follows reads
+// this kernel's output from row 0 up (measured inside the encoder step: 27.6 -> 25.3 ms per 960 launches).
 constexpr int kBulkWarps = 16;
 
 __device__ __forceinline__ void bulk_load_row(uint32_t dst, const float *src, uint32_t bytes, uint32_t bar) {
@@ -278,7 +281,7 @@ layernorm_bulk_kernel(const float *__restrict__ x, const float *__restrict__ gam
       const int64_t r = first + j * nwarps;
       if (r < rows) {
         tc::mbar_expect_tx(my_bar + 8 * j, row_bytes);
-        bulk_load_row(my_buf + j * row_bytes, x + r * len, row_bytes, my_bar + 8 * j);
+        bulk_load_row(my_buf + j * row_bytes, x + (rows - 1 - r) * len, row_bytes, my_bar + 8 * j);
       }
     }
   }
@@ -304,7 +307,7 @@ layernorm_bulk_kernel(const float *__restrict__ x, const float *__restrict__ gam
       if (next < rows) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         tc::mbar_expect_tx(my_bar + 8 * slot, row_bytes);
-        bulk_load_row(my_buf + slot * row_bytes, x + next * len, row_bytes, my_bar + 8 * slot);
+        bulk_load_row(my_buf + slot * row_bytes, x + (rows - 1 - next) * len, row_bytes, my_bar + 8 * slot);
       }
     }
     const float mean = warp_sum(s) / (float)len;  // ReduceMean
@@ -318,7 +321,7 @@ layernorm_bulk_kernel(const float *__restrict__ x, const float *__restrict__ gam
     }
     const float var = warp_sum(q) / (float)len;  // ReduceMean
     const float inv = 1.0f / sqrtf(var + eps);   // Add eps, Sqrt; Div as one reciprocal per row (see above)
-    float *yr = y + row * len;
+    float *yr = y + (rows - 1 - row) * len;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = lane + 32 * i;
@@ -327,7 +330,7 @@ layernorm_bulk_kernel(const float *__restrict__ x, const float *__restrict__ gam
         o.x = v[i].x * inv; o.y = v[i].y * inv; o.z = v[i].z * inv; o.w = v[i].w * inv;
         if (gamma) { o.x *= g[i].x; o.y *= g[i].y; o.z *= g[i].z; o.w *= g[i].w; }  // Mul
         if (beta) { o.x += b[i].x; o.y += b[i].y; o.z += b[i].z; o.w += b[i].w; }    // Add
-        st_stream4(yr + 4 * c, o);
+        *reinterpret_cast<float4 *>(yr + 4 * c) = o;
       }
     }
     if (++slot == depth) { slot = 0; ph ^= 1; }
